@@ -48,7 +48,14 @@ LATENT_ATTENTION_NAMES = (("q", "mix.q"), ("down", "mix.dkv"), ("latent_norm", "
 RELU2_NAMES = (("up", "mlp.up"), ("down", "mlp.down"))
 MOE_GROUPED_NAMES = (("expert", "mlp.e{}"), ("gate", "gate"), ("up", "up"), ("down", "down"), ("router", "mlp.router"),
                      ("correction", "mlp.correction"), ("shared", "mlp.shared"))
-MIXER_NAMES = {"diff_attention": DIFF_ATTENTION_NAMES, "hgrn2": HGRN2_NAMES, "latent_attention": LATENT_ATTENTION_NAMES}
+NORMED_ATTENTION_NAMES = (("q", "mix.q"), ("k", "mix.k"), ("v", "mix.v"), ("o", "mix.o"), ("gate", "mix.g"),
+                          ("q_bias", "mix.q.b"), ("k_bias", "mix.k.b"), ("v_bias", "mix.v.b"),
+                          ("q_norm", "mix.q.norm"), ("k_norm", "mix.k.norm"))
+RGLRU_NAMES = (("y", "mix.y"), ("y_bias", "mix.y.b"), ("x", "mix.x"), ("x_bias", "mix.x.b"), ("conv", "mix.conv"),
+               ("conv_bias", "mix.conv.b"), ("ra", "mix.ra"), ("ra_bias", "mix.ra.b"), ("ri", "mix.ri"),
+               ("ri_bias", "mix.ri.b"), ("lam", "mix.lam"), ("o", "mix.o"))
+MIXER_NAMES = {"diff_attention": DIFF_ATTENTION_NAMES, "hgrn2": HGRN2_NAMES, "latent_attention": LATENT_ATTENTION_NAMES,
+               "normed_attention": NORMED_ATTENTION_NAMES, "rglru": RGLRU_NAMES, "parallel": ()}
 FEED_FORWARD_NAMES = {"moe_swiglu": MOE_NAMES, "relu2": RELU2_NAMES, "moe_grouped": MOE_GROUPED_NAMES}
 
 
@@ -65,11 +72,16 @@ class PositionSpec:
     original length, lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), rotary_dim - 1) and
     ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i's frequency is f_i (1 - ramp_i) + f_i / factor * ramp_i,
     and cos and sin are multiplied by 0.1 ln(factor) + 1.
+
+    ``bands`` = (factor, low, high, original) scales by bands of the wavelength l = 2 pi / f instead: waves shorter than
+    original / high keep their frequency, waves longer than original / low get it divided by ``factor``, and in between
+    f becomes (1 - s) f / factor + s f with s = (original / l - low) / (high - low); the amplitude stays 1.
     """
     kind: str
     theta: float
     rotary_dim: int
     yarn: Optional[Tuple[float, float, float, float]] = None
+    bands: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -107,6 +119,24 @@ class MixerSpec:
     query), its value Wuv_n c (``value_dim`` wide).  ``position`` turns the ``rot_dim`` parts of queries and keys
     (its ``rotary_dim`` <= ``rot_dim``).  ``out_gate``: head n's result is multiplied by sigmoid of the n-th row of
     one more product of the mixer's input.  Causal softmax over all keys, ``scale`` as given.
+
+    kind "normed_attention": grouped-query attention whose queries and keys are normed.  ``qk_norm_kind``
+    "projection": an RMS norm with a weight over the whole query projection (all heads at once) and over the whole key
+    projection, before the rotation; "head_unit": every head of q and k divided by its root mean square (no weight)
+    after the rotation; "": none.  ``value_from_key``: there is no value projection, a key's value is the key as it
+    was projected (before norm and rotation).  ``sink``: the softmax's denominator has one more term exp(0) without a
+    value.  ``out_gate`` as above.  ``borrows_cache``: the layer has no key or value tensors at all and reads the cache
+    another schedule entry writes (its ``ScheduleEntry.write_cache`` is False).  ``keep_window``: how many keys the
+    cache keeps (the largest window of the layers that read it; None where any reads all keys); ``window`` is what
+    this layer's own mask lets it see.  q, k and v have biases where ``qkv_bias`` says so.
+
+    kind "rglru": a gated linear recurrence over ``rec_width`` channels: a gate branch y = gelu_tanh(Wy h + b) and a
+    recurrent branch u = conv(Wx h + b) (a causal convolution of ``conv_taps`` taps per channel, with a bias); per
+    block of rec_width / ``rec_blocks`` channels r = sigmoid(Ra u + b), i = sigmoid(Ri u + b);
+    a = exp(-``rec_slope`` r softplus(lam)); S <- a S + sqrt(1 - a^2) i u; result Wo (S * y).
+
+    kind "parallel": the mixers of ``branches`` read the same input side by side; the result is the sum of their
+    results times ``branch_scales``.  Branch b's tensors carry the leaf names of its own spec.
     """
     kind: str
     hidden: int
@@ -125,7 +155,17 @@ class MixerSpec:
     diff: float = 0.0
     rot_dim: int = 0                  # latent attention: width of the rotated part of a query / key
     latent_dim: int = 0               # latent attention: width of the cached latent
-    out_gate: bool = False            # latent attention: a sigmoid gate per head on the result
+    out_gate: bool = False            # a sigmoid gate per head on the result
+    qk_norm_kind: str = ""            # normed attention: "", "projection" or "head_unit"
+    value_from_key: bool = False
+    sink: bool = False
+    borrows_cache: bool = False
+    keep_window: Optional[int] = None
+    rec_width: int = 0
+    rec_blocks: int = 1
+    rec_slope: float = 8.0
+    branches: Tuple["MixerSpec", ...] = ()
+    branch_scales: Tuple[float, ...] = ()
     # free-form extras for mixers defined outside the framework
     extra: Tuple[Tuple[str, object], ...] = ()
     # role -> leaf name under the block's prefix (see ATTENTION_NAMES); roles not given keep the default
@@ -193,6 +233,8 @@ class BlockSpec:
     x += norm1(mixer(x) * sigmoid(G1 x + b1)); x += norm2(ffn(x) * sigmoid(G2 x + b2)); the gates are
     there where ``mixer_gate_name`` / ``ffn_gate_name`` are given (bias: that name + ``gate_bias_suffix``),
     and ``ffn`` may be None (a layer with a mixer only).
+    With ``residual_scale`` = m the sublayers' results enter the residual stream times m:
+    x += m mixer(norm1(x)); x += m ffn(norm2(x)).
     kind "hyper_prenorm": the residual is ``streams`` vectors per token.  Sublayer q (1: mixer, 2: feed-forward) has
     three small tensors under ``hyper_names[q-1]``: ``.in`` [S], ``.mix`` [S, S] (from, to), ``.out`` [S];
     u = sum_s in[s] x_s; y = sublayer(norm_q(u)); x_r <- sum_s mix[s, r] x_s + out[r] y for all r at once.
@@ -211,6 +253,7 @@ class BlockSpec:
     gate_bias_suffix: str = ".b"
     streams: int = 0
     hyper_names: Tuple[str, str] = ("hc1", "hc2")
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)

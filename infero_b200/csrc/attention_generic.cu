@@ -25,8 +25,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                          const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tok_entry, const int* __restrict__ positions,
-                         int n_tokens, int n_heads, int n_kv, int head_dim, int page_size,
-                         int window, float scale) {
+                         int n_tokens, int n_heads, int n_kv, int head_dim, int value_dim, int page_size,
+                         int window, float scale, int sink) {
     __shared__ float q_s[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -42,7 +42,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     for (int i = lane; i < head_dim; i += 32) q_s[warp][i] = to_f32(qrow[i]);
     __syncwarp();
 
-    float m = -CUDART_INF_F, l = 0.f;
+    // a sink is one more term of the softmax's sum, with score 0 and no value: the running maximum and sum start
+    // as if that key had been seen
+    float m = sink ? 0.f : -CUDART_INF_F, l = sink ? 1.f : 0.f;
     float acc[MAX_D / 32];
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
@@ -55,8 +57,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         if (valid) {
             const int page = table[j / page_size];
             if (page >= 0) {
-                row = (((long long)page * n_kv + kvh) * page_size + (j % page_size)) * head_dim;
-                const T* kr = k_cache + row;
+                row = ((long long)page * n_kv + kvh) * page_size + (j % page_size);
+                const T* kr = k_cache + row * head_dim;
                 float d = 0.f;
                 for (int i = 0; i < head_dim; ++i) d = fmaf(q_s[warp][i], to_f32(kr[i]), d);
                 s = d * scale;
@@ -73,21 +75,21 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long rj = __shfl_sync(0xffffffffu, row, jj);
             if (rj < 0) continue;                      // uniform across the warp
-            const T* vr = v_cache + rj;
+            const T* vr = v_cache + rj * value_dim;
 #pragma unroll
             for (int i = 0; i < MAX_D / 32; ++i) {
                 const int dd = i * 32 + lane;
-                if (dd < head_dim) acc[i] = fmaf(pj, to_f32(vr[dd]), acc[i]);
+                if (dd < value_dim) acc[i] = fmaf(pj, to_f32(vr[dd]), acc[i]);
             }
         }
         m = m_new;
     }
-    T* orow = out + (size_t)t * out_stride + (size_t)h * head_dim;
+    T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int dd = i * 32 + lane;
-        if (dd < head_dim) orow[dd] = from_f32<T>(acc[i] * inv);
+        if (dd < value_dim) orow[dd] = from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -95,25 +97,38 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 
 extern "C" {
 
-int infero_attention_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                             const void* v_cache, int dtype, const int* block_table, int max_blocks,
-                             const int* tok_entry, const int* positions, int n_tokens, int n_heads,
-                             int n_kv, int head_dim, int page_size, int window, float scale,
-                             cudaStream_t stream) {
+// Keys of width head_dim, values of width value_dim (the cache's two arrays have their own row widths); ``sink``:
+// the softmax's denominator has one more term exp(0), which carries no value.
+int infero_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                const void* v_cache, int dtype, const int* block_table, int max_blocks,
+                                const int* tok_entry, const int* positions, int n_tokens, int n_heads,
+                                int n_kv, int head_dim, int value_dim, int page_size, int window, float scale,
+                                int sink, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(head_dim >= 1 && head_dim <= MAX_D, "attention: head_dim %d outside 1..%d", head_dim, MAX_D);
+    INFERO_REQUIRE(value_dim >= 1 && value_dim <= MAX_D, "attention: value width %d outside 1..%d", value_dim, MAX_D);
     INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "attention: %d heads not a multiple of %d kv heads", n_heads, n_kv);
     const long long items = (long long)n_tokens * n_heads;
     const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
     if (dtype == INFERO_F32)
         attention_generic_kernel<float><<<blocks, WARPS * 32, 0, stream>>>((const float*)q, q_stride, (float*)out,
             out_stride, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks, tok_entry,
-            positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale);
+            positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size, window, scale, sink);
     else
         attention_generic_kernel<bf16><<<blocks, WARPS * 32, 0, stream>>>((const bf16*)q, q_stride, (bf16*)out,
             out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, tok_entry,
-            positions, n_tokens, n_heads, n_kv, head_dim, page_size, window, scale);
+            positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size, window, scale, sink);
     return infero_check_launch("attention_generic");
+}
+
+int infero_attention_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                             const void* v_cache, int dtype, const int* block_table, int max_blocks,
+                             const int* tok_entry, const int* positions, int n_tokens, int n_heads,
+                             int n_kv, int head_dim, int page_size, int window, float scale,
+                             cudaStream_t stream) {
+    return infero_attention_generic_ex(q, q_stride, out, out_stride, k_cache, v_cache, dtype, block_table, max_blocks,
+                                       tok_entry, positions, n_tokens, n_heads, n_kv, head_dim, head_dim, page_size,
+                                       window, scale, 0, stream);
 }
 
 }  // extern "C"

@@ -68,7 +68,7 @@ template <typename TD, typename TO, int VEC>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int splits,
                                    long long split_stride, const void* __restrict__ dbias, int dbias_dtype,
                                    const void* __restrict__ w, int wdtype, float eps,
-                                   TO* __restrict__ out, const int* __restrict__ rows, int d) {
+                                   TO* __restrict__ out, const int* __restrict__ rows, int d, float ds) {
     __shared__ float red[32];
     TL_BEGIN();
     pdl_launch_dependents();
@@ -100,12 +100,12 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
                         if (s0 + k < splits) load4(dr + (size_t)(s0 + k) * split_stride + i, t[k]);
 #pragma unroll
                     for (int k = 0; k < 8; ++k)
-                        if (s0 + k < splits) { v[0] += t[k][0]; v[1] += t[k][1]; v[2] += t[k][2]; v[3] += t[k][3]; }
+                        if (s0 + k < splits) { v[0] = fmaf(ds, t[k][0], v[0]); v[1] = fmaf(ds, t[k][1], v[1]); v[2] = fmaf(ds, t[k][2], v[2]); v[3] = fmaf(ds, t[k][3], v[3]); }
                 }
                 if (dbias) {
                     float t[4];
                     load4_any(dbias, dbias_dtype, i, t);
-                    v[0] += t[0]; v[1] += t[1]; v[2] += t[2]; v[3] += t[3];
+                    v[0] = fmaf(ds, t[0], v[0]); v[1] = fmaf(ds, t[1], v[1]); v[2] = fmaf(ds, t[2], v[2]); v[3] = fmaf(ds, t[3], v[3]);
                 }
             }
             store4(vbuf + i, v);
@@ -115,8 +115,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
             float v = xr[i];
             if (dr) {
-                for (int s = 0; s < splits; ++s) v += to_f32(dr[(size_t)s * split_stride + i]);
-                if (dbias) v += load_any(dbias, dbias_dtype, i);
+                for (int s = 0; s < splits; ++s) v = fmaf(ds, to_f32(dr[(size_t)s * split_stride + i]), v);
+                if (dbias) v = fmaf(ds, load_any(dbias, dbias_dtype, i), v);
             }
             vbuf[i] = v;
             ss = fmaf(v, v, ss);
@@ -154,7 +154,7 @@ template <typename TD, typename TO>
 __global__ void __launch_bounds__(1024, 2) add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                         const void* __restrict__ dbias, int dbias_dtype,
                                         const void* __restrict__ w, int wdtype, float eps,
-                                        TO* __restrict__ out, int n_rows, int d) {
+                                        TO* __restrict__ out, int n_rows, int d, float ds) {
     __shared__ float red[32];
     TL_BEGIN();
     pdl_launch_dependents();
@@ -175,8 +175,8 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_rows_kernel(float* __rest
     for (; r < n_rows; r += gridDim.x) {
         float v[4] = {xv[0], xv[1], xv[2], xv[3]};
         if (delta) {
-            v[0] += dv[0]; v[1] += dv[1]; v[2] += dv[2]; v[3] += dv[3];
-            if (dbias) { v[0] += bb[0]; v[1] += bb[1]; v[2] += bb[2]; v[3] += bb[3]; }
+            v[0] = fmaf(ds, dv[0], v[0]); v[1] = fmaf(ds, dv[1], v[1]); v[2] = fmaf(ds, dv[2], v[2]); v[3] = fmaf(ds, dv[3], v[3]);
+            if (dbias) { v[0] = fmaf(ds, bb[0], v[0]); v[1] = fmaf(ds, bb[1], v[1]); v[2] = fmaf(ds, bb[2], v[2]); v[3] = fmaf(ds, bb[3], v[3]); }
         }
         const int rn = r + gridDim.x;
         if (rn < n_rows && mine) {                   // the next row, before this one is reduced
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_ring_kernel(float* __rest
                                                                    const void* __restrict__ dbias, int dbias_dtype,
                                                                    const void* __restrict__ w, int wdtype, float eps,
                                                                    TO* __restrict__ out, int n_rows, int d, int ring,
-                                                                   int* __restrict__ err_flag) {
+                                                                   int* __restrict__ err_flag, float ds) {
     extern __shared__ __align__(16) uint8_t ring_mem[];
     __shared__ float red[32];
     __shared__ uint64_t full[8];
@@ -262,8 +262,8 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_ring_kernel(float* __rest
             if (delta) {
                 float dv[4];
                 load4(reinterpret_cast<const TD*>(st + x_bytes) + i, dv);
-                v[0] += dv[0]; v[1] += dv[1]; v[2] += dv[2]; v[3] += dv[3];
-                if (dbias) { v[0] += bb[0]; v[1] += bb[1]; v[2] += bb[2]; v[3] += bb[3]; }
+                v[0] = fmaf(ds, dv[0], v[0]); v[1] = fmaf(ds, dv[1], v[1]); v[2] = fmaf(ds, dv[2], v[2]); v[3] = fmaf(ds, dv[3], v[3]);
+                if (dbias) { v[0] = fmaf(ds, bb[0], v[0]); v[1] = fmaf(ds, bb[1], v[1]); v[2] = fmaf(ds, bb[2], v[2]); v[3] = fmaf(ds, bb[3], v[3]); }
             }
         }
         float ss = 0.f;
@@ -373,10 +373,12 @@ int infero_embed_gather(const void* table, int table_dtype, const int* ids, cons
 // delta may be null (plain norm); rows may be null (all rows, residual written back).
 // delta: delta_splits arrays of [rows of x, d], split_stride elements apart, summed in
 // ascending order, plus dbias (nullable) -- the few-token matrix kernel's partial products.
-int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_splits, long long split_stride,
-                       const void* dbias, int dbias_dtype, const void* w, int w_dtype,
-                       float eps, void* out, int out_dtype, const int* rows, int n_rows, int d,
-                       cudaStream_t stream) {
+// ``ds``: what the delta is multiplied by as it is added (a layer whose sublayers' results enter the residual
+// stream times a constant); 1 adds it as it is, bit for bit as without the factor.
+int infero_add_rmsnorm_scaled(float* x, const void* delta, int delta_dtype, int delta_splits, long long split_stride,
+                              const void* dbias, int dbias_dtype, const void* w, int w_dtype,
+                              float eps, void* out, int out_dtype, const int* rows, int n_rows, int d, float ds,
+                              cudaStream_t stream) {
     if (n_rows == 0) return 0;
     INFERO_REQUIRE(d > 0 && (size_t)d * 4 <= 160 * 1024, "add_rmsnorm: width %d not supported (1..40960)", d);
     INFERO_REQUIRE(delta_splits >= 1, "add_rmsnorm: %d splits", delta_splits);
@@ -417,7 +419,7 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
                 if (ring_bytes > 48 * 1024)                                                      \
                     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes); \
                 launch_pdl(k, dim3(blocks), dim3(threads), ring_bytes, stream, x, (const TD*)delta, dbias, dbias_dtype, \
-                           w, w_dtype, eps, (TO*)out, n_rows, d, ring, err);                      \
+                           w, w_dtype, eps, (TO*)out, n_rows, d, ring, err, ds);                      \
             } while (0)
             if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH_RING(float, float);
             else if (delta_dtype == INFERO_BF16 && out_dtype == INFERO_BF16) LAUNCH_RING(bf16, bf16);
@@ -428,7 +430,7 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
         }
 #define LAUNCH_ROWS(TD, TO)                                                                      \
         launch_pdl(add_rmsnorm_rows_kernel<TD, TO>, dim3(blocks), dim3(threads), 0, stream, x, (const TD*)delta, dbias, \
-                   dbias_dtype, w, w_dtype, eps, (TO*)out, n_rows, d)
+                   dbias_dtype, w, w_dtype, eps, (TO*)out, n_rows, d, ds)
         if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH_ROWS(float, float);
         else if (delta_dtype == INFERO_BF16 && out_dtype == INFERO_BF16) LAUNCH_ROWS(bf16, bf16);
         else if (delta_dtype == INFERO_F32 && out_dtype == INFERO_BF16) LAUNCH_ROWS(float, bf16);
@@ -443,13 +445,13 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
             if (smem > 48 * 1024)                                                               \
                 cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             launch_pdl(k, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta, delta_splits,   \
-                       split_stride, dbias, dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);            \
+                       split_stride, dbias, dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d, ds);            \
         } else {                                                                                \
             auto k = add_rmsnorm_kernel<TD, TO, 1>;                                             \
             if (smem > 48 * 1024)                                                               \
                 cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             launch_pdl(k, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta, delta_splits,   \
-                       split_stride, dbias, dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);            \
+                       split_stride, dbias, dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d, ds);            \
         }                                                                                       \
     } while (0)
     if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH(float, float);
@@ -458,6 +460,14 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
     else LAUNCH(bf16, float);
 #undef LAUNCH
     return infero_check_launch("add_rmsnorm");
+}
+
+int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_splits, long long split_stride,
+                       const void* dbias, int dbias_dtype, const void* w, int w_dtype,
+                       float eps, void* out, int out_dtype, const int* rows, int n_rows, int d,
+                       cudaStream_t stream) {
+    return infero_add_rmsnorm_scaled(x, delta, delta_dtype, delta_splits, split_stride, dbias, dbias_dtype, w, w_dtype, eps,
+                                     out, out_dtype, rows, n_rows, d, 1.0f, stream);
 }
 
 // gate_up: splits arrays of [n_tokens, 2 * ff] (dtype, gate and up alternating), split_stride elements apart.  out has

@@ -146,11 +146,21 @@ class Partials:
         return out
 
 
+class Scaled:
+    """A sublayer's result that enters the residual stream times a constant: ``value`` (a tensor or ``Partials``)
+    and ``scale``.  The norm kernel that adds the pending result multiplies as it adds."""
+
+    def __init__(self, value, scale: float):
+        self.value, self.scale = value, float(scale)
+
+
 def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-    """x += delta (if given; 32-bit), out = rmsnorm(x) * weight.  ``delta`` is a tensor or
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta_scale: float = 1.0) -> None:
+    """x += delta_scale * delta (if given; 32-bit), out = rmsnorm(x) * weight.  ``delta`` is a tensor or
     ``Partials``.  With ``rows`` only those rows are normalised (out has len(rows) rows) and x
     is left as it is."""
+    if isinstance(delta, Scaled):
+        delta, delta_scale = delta.value, delta_scale * delta.scale
     if hasattr(delta, "as_partials"):          # left by the native block launcher in its scratch arena
         delta = delta.as_partials()
     d = x.shape[1]
@@ -167,12 +177,12 @@ def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float,
         assert tuple(delta.shape) == tuple(x.shape)
     elif delta is not None:
         assert delta.shape == x.shape and delta.is_contiguous()
-    _check(lib().infero_add_rmsnorm(_ptr(x), _ptr(data), c_int(_dt(data) if data is not None else F32),
-                                    c_int(splits), ctypes.c_longlong(stride), _ptr(dbias),
-                                    c_int(_dt(dbias) if dbias is not None else F32),
-                                    _ptr(weight), c_int(_dt(weight)), c_float(eps), _ptr(out), c_int(_dt(out)),
-                                    _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(d),
-                                    _stream()))
+    _check(lib().infero_add_rmsnorm_scaled(_ptr(x), _ptr(data), c_int(_dt(data) if data is not None else F32),
+                                           c_int(splits), ctypes.c_longlong(stride), _ptr(dbias),
+                                           c_int(_dt(dbias) if dbias is not None else F32),
+                                           _ptr(weight), c_int(_dt(weight)), c_float(eps), _ptr(out), c_int(_dt(out)),
+                                           _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(d),
+                                           c_float(delta_scale), _stream()))
 
 
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
@@ -260,16 +270,18 @@ def rope_cache_partials(qkv: Partials, q_out: torch.Tensor, positions: torch.Ten
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_table: torch.Tensor, tok_entry: torch.Tensor, positions: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
-                      scale: float) -> None:
-    """q: [T, >= H*D] view (row stride free), out [T, H*D]."""
+                      scale: float, value_dim: int = 0, sink: bool = False) -> None:
+    """q: [T, >= H*D] view (row stride free), out [T, H*V] with V = ``value_dim`` (0: the keys' width).  ``sink``: one
+    more term exp(0) in the softmax's sum, without a value."""
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
-    _check(lib().infero_attention_generic(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
-                                          _ptr(k_cache), _ptr(v_cache), c_int(_dt(q)),
-                                          _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]),
-                                          _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),
-                                          c_int(T), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-                                          c_int(page_size), c_int(window or 0), c_float(scale), _stream()))
+    _check(lib().infero_attention_generic_ex(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
+                                             _ptr(k_cache), _ptr(v_cache), c_int(_dt(q)),
+                                             _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]),
+                                             _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),
+                                             c_int(T), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+                                             c_int(value_dim or head_dim), c_int(page_size), c_int(window or 0),
+                                             c_float(scale), c_int(1 if sink else 0), _stream()))
 
 
 # ---- sampling --------------------------------------------------------------------------------

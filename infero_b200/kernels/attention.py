@@ -199,3 +199,14 @@ def _batch_shape(ctx):
         except AttributeError:          # a context that takes no new attributes
             pass
     return memo
+
+
+def paged_attention_ex(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, sink: bool) -> None:
+    """Attention with values of their own width and, optionally, a sink (one more term exp(0) in the softmax's sum, without
+    a value).  q [T, H*D] rotated queries; out [T, H*V].  Equal widths without a sink take the same kernels as
+    ``paged_attention``; the rest runs on the any-type kernel."""
+    if not sink and value_dim == head_dim:
+        paged_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, window, scale)
+        return
+    attention_generic(q, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim, kv.page_size,
+                      window, scale, value_dim=value_dim, sink=sink)

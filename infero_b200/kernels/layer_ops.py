@@ -332,3 +332,73 @@ def streams_fill(x: torch.Tensor, xs: torch.Tensor) -> None:
     T, S, d = xs.shape
     assert x.dtype == xs.dtype == torch.float32 and x.is_contiguous() and xs.is_contiguous() and tuple(x.shape) == (T, d)
     _check(lib().infero_streams_fill(_ptr(x), _ptr(xs), c_int(T), c_int(S), c_int(d), _stream()))
+
+
+# ---- normed attention, gated linear recurrence (csrc/qk_prepare.cu, rglru.cu) ------------------------------------
+def qk_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, norm_mode: int, q_norm_w, k_norm_w, eps: float,
+               freq64: Optional[torch.Tensor], amp: float, positions, tok_entry, block_table, page_size: int,
+               q_out: torch.Tensor, k_cache, v_cache, H: int, G: int, D: int, V: int, write_cache: bool = True) -> None:
+    """From the 32-bit product row of every token (``proj`` [T, >= ...], columns ``q_off`` / ``k_off`` / ``v_off``; a
+    negative ``v_off``: the values are the keys as projected) to normed, rotated queries in ``q_out`` [T, H*D] and keys and
+    values in the token's page.  ``norm_mode`` 0 none, 1 weighted RMS over the whole projection before the rotation,
+    2 unit RMS per head after it.  ``freq64`` float64 [rot/2] (None: no rotation), ``amp`` multiplies cos and sin."""
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.shape == (T, H * D)
+    rot = 0
+    if freq64 is not None:
+        assert freq64.dtype == torch.float64 and freq64.is_contiguous()
+        rot = 2 * freq64.numel()
+    if write_cache:
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == q_out.dtype == v_cache.dtype
+        assert k_cache.shape[1:] == (G, page_size, D) and v_cache.shape[1:] == (G, page_size, V)
+    if norm_mode == 1:
+        assert q_norm_w.numel() == H * D and (not write_cache or k_norm_w.numel() == G * D)
+        assert k_norm_w is None or k_norm_w.dtype == q_norm_w.dtype
+    _check(lib().infero_qk_prepare(
+        _ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), c_int(norm_mode), _ptr(q_norm_w),
+        _ptr(k_norm_w), c_int(_dt(q_norm_w) if q_norm_w is not None else 0), c_float(eps), _ptr(freq64), c_int(rot),
+        c_float(amp), _ptr(_i32(positions, "positions")), _ptr(_i32(tok_entry, "tok_entry")),
+        _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]), c_int(page_size), _ptr(q_out),
+        c_int(q_out.stride(0)), _ptr(k_cache if write_cache else None), _ptr(v_cache if write_cache else None),
+        c_int(_dt(q_out)), c_int(1 if write_cache else 0), c_int(T), c_int(H), c_int(G), c_int(D), c_int(V), _stream()))
+
+
+def head_gate(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, H: int, V: int, scale: float = 1.0) -> None:
+    """out[t, h*V + v] = a[t, h*V + v] * sigmoid(gate[t, h]) * scale (no gate: only the factor); gate float32, a column
+    slice allowed; ``out`` may be ``a`` or a column slice of a wider array."""
+    T = a.shape[0]
+    assert a.shape == (T, H * V) and out.shape == (T, H * V) and a.stride(1) == 1 and out.stride(1) == 1 and a.dtype == out.dtype
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == (T, H) and gate.stride(1) == 1)
+    _check(lib().infero_head_gate(_ptr(a), c_int(a.stride(0)), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
+                                  _ptr(out), c_int(out.stride(0)), c_int(_dt(a)), c_int(T), c_int(H), c_int(V), c_float(scale),
+                                  _stream()))
+
+
+def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], ra, ri,
+          ra_b: torch.Tensor, ri_b: torch.Tensor, lam: torch.Tensor, slope: float, state: torch.Tensor, tok_entry,
+          entry_q_start, entry_q_len, entry_slot, n_entries: int, out: torch.Tensor, blocks: int, scale: float = 1.0) -> None:
+    """The gated linear recurrence of every request of the step over its new tokens; see csrc/rglru.cu.  ``proj`` float32
+    [T, >= ...] holds the gate branch at ``y_off`` and the recurrent branch at ``x_off`` (C columns each, biases added);
+    ``conv_w`` float32 [C, taps]; ``ra`` / ``ri`` [blocks, C/blocks, C/blocks] (float32 or bf16); ``state`` float32
+    [slots, taps, C] (rows 0..taps-2 the convolution's last inputs, row taps-1 the recurrent state); ``out`` [T, C] (a
+    column slice allowed) receives S * gelu_tanh(y) * scale."""
+    T = proj.shape[0]
+    C, taps = conv_w.shape
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.shape == (T, C) and out.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps, C)
+    _f32(conv_w, "conv_w"), _f32(conv_b, "conv_b"), _f32(ra_b, "ra_b"), _f32(ri_b, "ri_b"), _f32(lam, "lam")
+    bs = C // blocks
+    assert ra.shape == (blocks, bs, bs) and ri.shape == (blocks, bs, bs) and ra.dtype == ri.dtype and ra.is_contiguous() and ri.is_contiguous()
+    u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    gates = torch.empty((T, 2 * C), dtype=torch.float32, device=proj.device)
+    L = lib()
+    _check(L.infero_rglru_conv(_ptr(proj), c_int(proj.stride(0)), c_int(x_off), _ptr(conv_w), _ptr(conv_b), c_int(taps),
+                               _ptr(state), _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(entry_q_start, "entry_q_start")),
+                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(u), c_int(T), c_int(C), _stream()))
+    _check(L.infero_rglru_gates(_ptr(u), _ptr(ra), _ptr(ri), c_int(_dt(ra)), _ptr(gates), c_int(T), c_int(C), c_int(blocks),
+                                _stream()))
+    _check(L.infero_rglru_scan(_ptr(proj), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(u), _ptr(gates), _ptr(ra_b),
+                               _ptr(ri_b), _ptr(lam), c_float(slope), c_int(taps), _ptr(state),
+                               _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
+                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(out), c_int(out.stride(0)), c_int(_dt(out)),
+                               c_int(n_entries), c_int(C), c_float(scale), _stream()))

@@ -11,6 +11,9 @@ from .hgrn2 import Hgrn2Mixer
 from .diff_attention import DiffAttention
 from .moe import GroupedMoe, MoeSwiGlu
 from .latent_attention import LatentAttention
+from .normed_attention import NormedAttention
+from .rglru import RgLruMixer
+from .parallel import ParallelMixer
 from .block import GatedPostNormBlock, HyperPreNormBlock, PreNormBlock
 
 register_part("norm", "rmsnorm", RmsNorm)
@@ -30,8 +33,11 @@ register_part("feed_forward", "relu2", Relu2Mlp)
 register_part("feed_forward", "glu", GluMlp)
 register_part("feed_forward", "moe_grouped", GroupedMoe)
 register_part("block", "hyper_prenorm", HyperPreNormBlock)
+register_part("mixer", "normed_attention", NormedAttention)
+register_part("mixer", "rglru", RgLruMixer)
+register_part("mixer", "parallel", ParallelMixer)
 
 __all__ = ["FeedForward", "KvCacheSpec", "Mixer", "Norm", "Part", "PositionEncoding", "StateSpec",
            "TensorDecl", "Linear", "RmsNorm", "ScalarRmsNorm", "RopeNeox", "RopeInterleaved", "SwiGluMlp", "GqaAttention",
            "Hgrn2Mixer", "DiffAttention", "MoeSwiGlu", "PreNormBlock", "GatedPostNormBlock", "LayerNorm", "GluMlp", "Relu2Mlp",
-           "GroupedMoe", "LatentAttention", "HyperPreNormBlock"]
+           "GroupedMoe", "LatentAttention", "HyperPreNormBlock", "NormedAttention", "RgLruMixer", "ParallelMixer"]

@@ -51,7 +51,9 @@ class PreNormBlock(Part):
         return native if native.wants(ctx) else None
 
     def forward(self, ctx, x, delta, slot):
-        native = self._native_for(ctx)
+        from .. import kernels as K
+        m = float(getattr(self.spec, "residual_scale", 1.0))
+        native = None if (m != 1.0 or isinstance(delta, K.Scaled)) else self._native_for(ctx)
         if native is not None:
             # the package's own parts in a bf16 step: the whole layer in one native call (same kernels,
             # same arguments, same order as below)
@@ -62,10 +64,13 @@ class PreNormBlock(Part):
             delta = delta.as_partials()
         h = self.mixer_norm.forward(ctx, x, delta)
         a = self.mixer.forward(ctx, h, slot)
+        if m != 1.0:
+            a = K.Scaled(a, m)               # the norm that adds it multiplies as it adds
         if self.ffn is None:
             return a
         h = self.ffn_norm.forward(ctx, x, a)
-        return self.ffn.forward(ctx, h)
+        f = self.ffn.forward(ctx, h)
+        return K.Scaled(f, m) if m != 1.0 else f
 
 
 class GatedPostNormBlock(Part):

@@ -133,6 +133,8 @@ class NativeBlock:
         b = self.block
         if type(b.mixer) is not GqaAttention or type(b.ffn) is not SwiGluMlp:
             return False
+        if float(getattr(b.spec, "residual_scale", 1.0)) != 1.0:
+            return False
         if type(b.mixer_norm) is not RmsNorm or type(b.ffn_norm) is not RmsNorm:
             return False
         if b.mixer.rope is not None and type(b.mixer.rope) is not RopeNeox:

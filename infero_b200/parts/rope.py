@@ -24,6 +24,24 @@ def yarn_stretch(inv, theta: float, dims: int, factor: float, original: float, f
     return inv / factor * ramp + inv * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+def band_scale(inv, factor: float, low: float, high: float, original: float):
+    """Frequencies scaled by bands of the wavelength l = 2 pi / f: waves shorter than original / high stay, waves longer
+    than original / low are divided by ``factor``, in between f becomes (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low).  64-bit on the host."""
+    import math
+    out = np.array(inv, dtype=np.float64)
+    for i, f in enumerate(inv):
+        wave = 2.0 * math.pi / f
+        if wave < original / high:
+            continue
+        if wave > original / low:
+            out[i] = f / factor
+        else:
+            s = (original / wave - low) / (high - low)
+            out[i] = (1.0 - s) * f / factor + s * f
+    return out
+
+
 class RopeNeox(PositionEncoding):
     """inv_freq[i] = theta^(-2i / rotary_dim), i < rotary_dim/2; angle = pos * inv_freq[i]
     (crates/kernels/src/cu/ops.cu:488-523).  The table is made on the host in 64-bit and
@@ -40,6 +58,8 @@ class RopeNeox(PositionEncoding):
         self.amplitude = 1.0
         if getattr(spec, "yarn", None):
             inv, self.amplitude = yarn_stretch(inv, spec.theta, spec.rotary_dim, *spec.yarn)
+        if getattr(spec, "bands", None):
+            inv = band_scale(inv, *spec.bands)
         self._inv_host = torch.from_numpy(inv.astype(np.float32))
         self._inv_host64 = torch.from_numpy(np.ascontiguousarray(inv, dtype=np.float64))
         self._inv_dev = {}

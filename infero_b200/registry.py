@@ -93,6 +93,8 @@ def _register_builtin() -> None:
     register_architecture("Vufizen", VufizenConfig.from_dict, lambda c: c.to_model_spec())
     from .config.gositar import GositarConfig
     register_architecture("Gositar", GositarConfig.from_dict, lambda c: c.to_model_spec())
+    from .config.banelix import BanelixConfig
+    register_architecture("Banelix", BanelixConfig.from_dict, lambda c: c.to_model_spec())
 
 
 _register_builtin()
