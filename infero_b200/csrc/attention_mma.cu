@@ -35,7 +35,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
                     const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
-                    int first_entry, int n_heads, int n_kv, int page_size, int window, float scale_log2) {
+                    int first_entry, int n_heads, int n_kv, int page_size, int window, float scale_log2, int sink) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
@@ -114,6 +114,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (sink) {                       // one more term 2^(0 - m) in the sum, with no value behind it
+        l0 += exp2f(-m[0]);
+        l1 += exp2f(-m[1]);
+    }
     const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
     bf16* orow0 = out + (size_t)(tok0 + wrow + g) * out_stride + (size_t)h * D;
     bf16* orow1 = orow0 + (size_t)8 * out_stride;
@@ -247,7 +251,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 // ascending order.  One warp per (token, head).
 __global__ void attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                     bf16* __restrict__ out, int out_stride, int tok_first, int n_tok, int n_heads,
-                                    int n_splits, int head_dim) {
+                                    int n_splits, int head_dim, int sink) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -262,6 +266,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial_o, const f
         const float ms = ml[s * 2];
         if (ms != -CUDART_INF_F) L += ml[s * 2 + 1] * exp2f(ms - M);
     }
+    if (sink) L += exp2f(-M);          // the sink's term, once for all splits
     const float inv = 1.0f / L;
     bf16* orow = out + (size_t)(tok_first + ti) * out_stride + (size_t)h * head_dim;
     for (int d = lane; d < head_dim; d += 32) {
@@ -278,7 +283,7 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache, const void* v_cache,
                    const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
                    const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv,
-                   int page_size, int window, float scale_log2, cudaStream_t stream) {
+                   int page_size, int window, float scale_log2, int sink, cudaStream_t stream) {
     auto kern = attn_prefill_kernel<D>;
     const int smem = 2 * 2 * tile_elems<D>(PF_KEYS) * 2;
     static bool configured = false;
@@ -289,7 +294,7 @@ int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const
     dim3 grid(n_tiles, n_heads);
     launch_pdl(kern, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, entry_q_start, entry_q_len,
-               entry_pos0, n_entries, first_entry, n_heads, n_kv, page_size, window, scale_log2);
+               entry_pos0, n_entries, first_entry, n_heads, n_kv, page_size, window, scale_log2, sink);
     return infero_check_launch("attn_prefill");
 }
 
@@ -338,21 +343,32 @@ int infero_attn_mma_supported(int head_dim, int page_size) {
 // Attention for requests first_entry .. n_entries - 1 of a step (bf16), each with any number
 // of new tokens.  n_tiles = sum over those requests of ceil(q_len / 64).  q / out rows are indexed by the
 // step's token index.
-int infero_attn_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                        const void* v_cache, const int* block_table, int max_blocks, const int* entry_q_start,
-                        const int* entry_q_len, const int* entry_pos0, int n_entries, int first_entry, int n_tiles,
-                        int n_heads, int n_kv, int head_dim, int page_size, int window, float scale,
-                        cudaStream_t stream) {
+// ``sink``: the softmax's sum has one more term exp(0) that carries no value.
+int infero_attn_prefill_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                             const void* v_cache, const int* block_table, int max_blocks, const int* entry_q_start,
+                             const int* entry_q_len, const int* entry_pos0, int n_entries, int first_entry, int n_tiles,
+                             int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int sink,
+                             cudaStream_t stream) {
     if (n_tiles == 0) return 0;
     INFERO_REQUIRE(infero_attn_mma_supported(head_dim, page_size), "attn_prefill: head_dim %d / page_size %d not supported", head_dim, page_size);
     INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0 && n_heads <= 65535, "attn_prefill: bad head counts %d / %d", n_heads, n_kv);
     INFERO_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0, "attn_prefill: odd row strides");
     const float sl2 = scale * 1.4426950408889634f;
-#define CALL(D_) launch_prefill<D_>(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, stream)
+#define CALL(D_) launch_prefill<D_>(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, sink, stream)
     DISPATCH_D(head_dim, CALL)
 #undef CALL
     infero_set_error("attn_prefill: head_dim %d has no instance", head_dim);
     return 1;
+}
+
+int infero_attn_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                        const void* v_cache, const int* block_table, int max_blocks, const int* entry_q_start,
+                        const int* entry_q_len, const int* entry_pos0, int n_entries, int first_entry, int n_tiles,
+                        int n_heads, int n_kv, int head_dim, int page_size, int window, float scale,
+                        cudaStream_t stream) {
+    return infero_attn_prefill_sink(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, entry_q_start,
+                                    entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads, n_kv, head_dim,
+                                    page_size, window, scale, 0, stream);
 }
 
 // Bytes of 32-bit scratch a decode call needs (partial outputs and their statistics).
@@ -363,11 +379,11 @@ long long infero_attn_decode_scratch(int n_tok, int n_heads, int head_dim, int n
 // Attention for n_tok single-token requests: tokens tok_first .. tok_first + n_tok - 1 of the
 // step.  chunk (keys per split, a multiple of 16) times n_splits must cover the longest
 // visible context.  scratch: infero_attn_decode_scratch bytes.
-int infero_attn_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                       const void* v_cache, const int* block_table, int max_blocks, const int* tok_entry,
-                       const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim,
-                       int page_size, int window, float scale, int chunk, int n_splits, void* scratch,
-                       cudaStream_t stream) {
+int infero_attn_decode_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                            const void* v_cache, const int* block_table, int max_blocks, const int* tok_entry,
+                            const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim,
+                            int page_size, int window, float scale, int chunk, int n_splits, void* scratch, int sink,
+                            cudaStream_t stream) {
     if (n_tok == 0) return 0;
     INFERO_REQUIRE(infero_attn_mma_supported(head_dim, page_size), "attn_decode: head_dim %d / page_size %d not supported", head_dim, page_size);
     INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "attn_decode: bad head counts %d / %d", n_heads, n_kv);
@@ -395,8 +411,18 @@ int infero_attn_decode(const void* q, int q_stride, void* out, int out_stride, c
     const int warps = n_tok * n_heads;
     const int blocks = (warps + 3) / 4;
     attn_combine_kernel<<<blocks, 128, 0, stream>>>(po, pml, (bf16*)out, out_stride, tok_first, n_tok, n_heads,
-                                                    n_splits, head_dim);
+                                                    n_splits, head_dim, sink);
     return infero_check_launch("attn_combine");
+}
+
+int infero_attn_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                       const void* v_cache, const int* block_table, int max_blocks, const int* tok_entry,
+                       const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim,
+                       int page_size, int window, float scale, int chunk, int n_splits, void* scratch,
+                       cudaStream_t stream) {
+    return infero_attn_decode_sink(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, tok_entry, positions,
+                                   tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits, scratch, 0,
+                                   stream);
 }
 
 }  // extern "C"

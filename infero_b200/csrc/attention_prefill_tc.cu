@@ -87,7 +87,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
                        const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
                        int first_entry, int n_tiles, int n_heads, int n_kv, int heads_per_cta, int page_size, int slice,
-                       int window, float scale_log2, int* __restrict__ err_flag) {
+                       int window, float scale_log2, int sink, int* __restrict__ err_flag) {
     using Plan = PfPlan<D>;
     constexpr int DB = Plan::DB, ST = Plan::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -385,7 +385,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok) {
             // every lane takes part in the TMEM loads (they are warp-wide); only lanes that own a
             // row of the portion store
-            const float inv = 1.0f / l;
+            // a sink: one more term 2^(0 - m) in the sum, with no value behind it
+            const float inv = 1.0f / (sink ? l + ex2(-m) : l);
             const uint32_t o_addr = head_tmem + Plan::O_COL;
             bf16* orow = out + (size_t)(tok0 + row_first + (valid ? r : 0)) * out_stride + (size_t)h * D;
 #pragma unroll 1
@@ -423,7 +424,7 @@ template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
            const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
            const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv, int page_size,
-           int slice, int window, float scale_log2, int* err, cudaStream_t stream) {
+           int slice, int window, float scale_log2, int sink, int* err, cudaStream_t stream) {
     using Plan = PfPlan<D>;
     // Two heads per CTA halve the key and value traffic, but a grid that does not fill the SMs that way
     // runs faster with one head per CTA: measured at 7B sizes 25 against 35 us at 1,024 tokens (128
@@ -448,7 +449,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     }
     launch_pdl(kern, dim3(n_kv * ((group + hpc - 1) / hpc), n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
                block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads,
-               n_kv, hpc, page_size, slice, window, scale_log2, err);
+               n_kv, hpc, page_size, slice, window, scale_log2, sink, err);
     return infero_check_launch("attn_prefill_tc");
 }
 
@@ -464,11 +465,12 @@ int infero_attn_prefill_tc_supported(int head_dim, int page_size, int q_stride, 
 // n_tiles = sum over the requests first_entry .. n_entries - 1 of ceil(q_len / 128).  q is
 // [n_tokens, >= n_heads * head_dim] bf16 with row stride q_stride; the caches are
 // [num_pages, n_kv, page_size, head_dim] bf16, contiguous; all 16-byte aligned.
-int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
-                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
-                           const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
-                           int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
-                           int window, float scale, cudaStream_t stream) {
+// ``sink``: the softmax's sum has one more term exp(0) that carries no value.
+int infero_attn_prefill_tc_sink(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                                const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                                const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
+                                int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
+                                int window, float scale, int sink, cudaStream_t stream) {
     if (n_tiles == 0) return 0;
     INFERO_REQUIRE(infero_attn_prefill_tc_supported(head_dim, page_size, q_stride, out_stride),
                    "attn_prefill_tc: head_dim %d / page_size %d / strides %d, %d not supported", head_dim, page_size,
@@ -490,9 +492,19 @@ int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out,
     const float sl2 = scale * 1.4426950408889634f;
     if (head_dim == 128)
         return launch<128>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
-                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, err, stream);
+                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, sink, err, stream);
     return launch<64>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
-                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, err, stream);
+                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, sink, err, stream);
+}
+
+int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                           const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
+                           int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
+                           int window, float scale, cudaStream_t stream) {
+    return infero_attn_prefill_tc_sink(q, q_stride, n_tokens, out, out_stride, k_cache, v_cache, num_pages, block_table,
+                                       max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles,
+                                       n_heads, n_kv, head_dim, page_size, window, scale, 0, stream);
 }
 
 }  // extern "C"

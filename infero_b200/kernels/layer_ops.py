@@ -374,31 +374,45 @@ def head_gate(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, 
                                   _stream()))
 
 
-def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], ra, ri,
+def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], w_gates: torch.Tensor,
           ra_b: torch.Tensor, ri_b: torch.Tensor, lam: torch.Tensor, slope: float, state: torch.Tensor, tok_entry,
-          entry_q_start, entry_q_len, entry_slot, n_entries: int, out: torch.Tensor, blocks: int, scale: float = 1.0) -> None:
+          entry_q_start, entry_q_len, entry_slot, n_entries: int, out: torch.Tensor, scale: float = 1.0,
+          max_q_len: int = 1, tensor_cores: bool = False) -> None:
     """The gated linear recurrence of every request of the step over its new tokens; see csrc/rglru.cu.  ``proj`` float32
     [T, >= ...] holds the gate branch at ``y_off`` and the recurrent branch at ``x_off`` (C columns each, biases added);
-    ``conv_w`` float32 [C, taps]; ``ra`` / ``ri`` [blocks, C/blocks, C/blocks] (float32 or bf16); ``state`` float32
-    [slots, taps, C] (rows 0..taps-2 the convolution's last inputs, row taps-1 the recurrent state); ``out`` [T, C] (a
-    column slice allowed) receives S * gelu_tanh(y) * scale."""
+    ``conv_w`` float32 [C, taps]; ``w_gates`` [blocks, 2 C/blocks, C/blocks] (float32 or bf16): per block the rows of Ra,
+    then those of Ri; ``state`` float32 [slots, taps, C] (rows 0..taps-2 the convolution's last inputs, row taps-1 the
+    recurrent state); ``out`` [T, C] (a column slice allowed) receives S * gelu_tanh(y) * scale.  ``max_q_len``: the
+    longest portion of the step.  ``tensor_cores``: the gate products of a long bf16 step run on the tensor-core product,
+    block by block, from u rounded to bf16 (32-bit sums); otherwise they are 32-bit throughout."""
     T = proj.shape[0]
     C, taps = conv_w.shape
+    blocks, two_bs, bs = w_gates.shape
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.shape == (T, C) and out.stride(1) == 1
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps, C)
+    assert blocks * bs == C and two_bs == 2 * bs and w_gates.is_contiguous()
     _f32(conv_w, "conv_w"), _f32(conv_b, "conv_b"), _f32(ra_b, "ra_b"), _f32(ri_b, "ri_b"), _f32(lam, "lam")
-    bs = C // blocks
-    assert ra.shape == (blocks, bs, bs) and ri.shape == (blocks, bs, bs) and ra.dtype == ri.dtype and ra.is_contiguous() and ri.is_contiguous()
     u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
     gates = torch.empty((T, 2 * C), dtype=torch.float32, device=proj.device)
+    use_tc = False
+    if tensor_cores and T > 256 and w_gates.dtype == torch.bfloat16 and bs % 8 == 0:
+        from . import tc_gemm
+        u16 = torch.empty((T, C), dtype=torch.bfloat16, device=proj.device)
+        use_tc = all(tc_gemm.supported(u16[:, b * bs:(b + 1) * bs], w_gates[b], gates[:, 2 * b * bs:2 * (b + 1) * bs])
+                     for b in (0, blocks - 1))
     L = lib()
     _check(L.infero_rglru_conv(_ptr(proj), c_int(proj.stride(0)), c_int(x_off), _ptr(conv_w), _ptr(conv_b), c_int(taps),
                                _ptr(state), _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(entry_q_start, "entry_q_start")),
-                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(u), c_int(T), c_int(C), _stream()))
-    _check(L.infero_rglru_gates(_ptr(u), _ptr(ra), _ptr(ri), c_int(_dt(ra)), _ptr(gates), c_int(T), c_int(C), c_int(blocks),
-                                _stream()))
+                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(u), _ptr(u16 if use_tc else None), c_int(T), c_int(C),
+                               _stream()))
+    if use_tc:
+        for b in range(blocks):
+            tc_gemm.gemm(u16[:, b * bs:(b + 1) * bs], w_gates[b], None, gates[:, 2 * b * bs:2 * (b + 1) * bs])
+    else:
+        _check(L.infero_rglru_gates(_ptr(u), _ptr(w_gates), c_int(_dt(w_gates)), _ptr(gates), c_int(T), c_int(C), c_int(blocks),
+                                    _stream()))
     _check(L.infero_rglru_scan(_ptr(proj), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(u), _ptr(gates), _ptr(ra_b),
                                _ptr(ri_b), _ptr(lam), c_float(slope), c_int(taps), _ptr(state),
                                _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
                                _ptr(_i32(entry_slot, "entry_slot")), _ptr(out), c_int(out.stride(0)), c_int(_dt(out)),
-                               c_int(n_entries), c_int(C), c_float(scale), _stream()))
+                               c_int(n_entries), c_int(C), c_int(blocks), c_int(max(1, int(max_q_len))), c_float(scale), _stream()))

@@ -61,9 +61,10 @@ class RgLruMixer(Mixer):
         self._bias = torch.cat([f32("y_bias"), f32("x_bias")]).contiguous()
         self.inp = Linear(self._rows, self._bias, f"{self.prefix}.yx")
         self.conv_w, self.conv_b = f32("conv"), f32("conv_bias")
-        self.ra, self.ri = tensors[self._n("ra", False)].contiguous(), tensors[self._n("ri", False)].contiguous()
-        if self.ra.dtype != self.ri.dtype:
-            self.ra, self.ri = self.ra.float(), self.ri.float()
+        ra, ri = tensors[self._n("ra", False)], tensors[self._n("ri", False)]
+        if ra.dtype != ri.dtype:
+            ra, ri = ra.float(), ri.float()
+        self.w_gates = torch.cat([ra, ri], dim=1).contiguous()         # [blocks, 2 bs, bs]: per block Ra's rows, then Ri's
         self.ra_b, self.ri_b = f32("ra_bias").reshape(-1), f32("ri_bias").reshape(-1)
         self.lam = f32("lam")
         self._out_w = tensors[self._n("o")]
@@ -80,9 +81,12 @@ class RgLruMixer(Mixer):
         return self.C
 
     def core(self, ctx, proj: torch.Tensor, off: int, slot, out: torch.Tensor, scale: float = 1.0) -> None:
-        L.rglru(proj, off, off + self.C, self.conv_w, self.conv_b, self.ra, self.ri, self.ra_b, self.ri_b, self.lam,
+        q_lens = getattr(ctx, "h_q_len", None)
+        longest = int(getattr(ctx, "max_q_len", 0)) or (int(q_lens.max()) if q_lens is not None and len(q_lens) else int(proj.shape[0]))
+        L.rglru(proj, off, off + self.C, self.conv_w, self.conv_b, self.w_gates, self.ra_b, self.ri_b, self.lam,
                 float(self.spec.rec_slope), ctx.state(slot.cache), ctx.tok_entry, ctx.entry_q_start, ctx.entry_q_len,
-                ctx.entry_slot, ctx.n_entries, out, self.blocks, scale)
+                ctx.entry_slot, ctx.n_entries, out, scale, max_q_len=longest,
+                tensor_cores=ctx.act_dtype == torch.bfloat16)
 
     def forward(self, ctx, h, slot):
         proj = self.inp.forward(h, out_dtype=torch.float32)
