@@ -284,10 +284,10 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="size of the timed prompt step (2,048 by default; 8,192 and more show attention over long contexts)")
     ap.add_argument("--designs", action="store_true",
-                    help="instead of the headline workload: Vufizen beside Qwen2 at equal layer sizes, prompt and decode "
+                    help="instead of the headline workload: one of the added designs (--design) beside Qwen2 at equal layer sizes, prompt and decode "
                          "steps and the kernels alone (infero_b200/tools/design_bench.py; its own JSON line)")
     ap.add_argument("--design-sizes", default="s,m")
-    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar"],
+    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar", "banelix"],
                     help="with --designs: which of the added designs runs beside Qwen2")
     args = ap.parse_args(argv)
 

@@ -75,9 +75,11 @@ class BanelixLayer:
 
 def _rot(m: Dict[str, Any], where: str, dim: int, keys: Tuple[str, ...]) -> BanelixRot:
     rot = m.get("rot")
+    if rot is None:                                   # no rotation at all
+        return BanelixRot(10000.0, 0, None)
     if not isinstance(rot, dict):
-        raise ConfigError(f"config.json: {where}.rot is missing")
-    dims = rot.get("dims")
+        raise ConfigError(f"config.json: {where}.rot is not an object")
+    dims = rot.get("dims", dim)
     if isinstance(dims, bool) or not isinstance(dims, int) or dims < 0 or dims % 2 or dims > dim:
         raise ConfigError(f"config.json: {where}.rot.dims {dims!r} must be even and at most dim {dim}")
     base = _number(rot, "base", where + ".rot") if dims else 10000.0
@@ -97,7 +99,8 @@ def _attention(m: Dict[str, Any], where: str, windowed: bool) -> BanelixAttentio
         raise ConfigError(f"config.json: {where}: {heads} heads are not a multiple of {kv} kv_heads")
     window, src = None, None
     if windowed:
-        window = _pos_int(m.get("mask") or {}, "size", where + ".mask")
+        if m.get("mask") is not None:                 # no mask key: every earlier token is seen
+            window = _pos_int(m["mask"], "size", where + ".mask")
         rot = _rot(m, where, dim, ("factor", "original", "fast", "slow"))
         if m.get("kv_from") is not None:
             src = m["kv_from"]
@@ -157,8 +160,9 @@ class BanelixConfig:
                 if rec.conv > 16:
                     raise ConfigError(f"config.json: {wr}: {rec.conv} taps, at most 16")
                 layers.append(BanelixLayer("parallel", _attention(left, where + ".mixer.left", False), rec,
-                                           _number(m, "left_scale", where + ".mixer", positive=False),
-                                           _number(m, "right_scale", where + ".mixer", positive=False), ff))
+                                           _number(m, "left_scale", where + ".mixer", positive=False) if m.get("left_scale") is not None else 1.0,
+                                           _number(m, "right_scale", where + ".mixer", positive=False) if m.get("right_scale") is not None else 1.0,
+                                           ff))
             else:
                 raise ConfigError(f"config.json: {where}.type {L.get('type')!r} is neither 'attention' nor 'parallel'")
         for i, L in enumerate(layers):
@@ -170,10 +174,10 @@ class BanelixConfig:
                 raise ConfigError(f"config.json: {where} {a.kv_from} must name an earlier layer")
             src = layers[a.kv_from]
             b = src.attention
-            if src.type != "attention" or b.kv_from is not None:
-                raise ConfigError(f"config.json: {where}: layer {a.kv_from} has no keys and values of its own kind")
-            if (b.kv_heads, b.dim, b.vdim, b.rot) != (a.kv_heads, a.dim, a.vdim, a.rot):
-                raise ConfigError(f"config.json: {where}: layer {a.kv_from}'s key/value heads, sizes and rotation differ")
+            if b.kv_from is not None:
+                raise ConfigError(f"config.json: {where}: layer {a.kv_from} has no keys and values of its own")
+            if (b.kv_heads, b.dim, b.vdim) != (a.kv_heads, a.dim, a.vdim):
+                raise ConfigError(f"config.json: {where}: layer {a.kv_from}'s key/value heads and sizes differ")
         return cls(vocab, width, eps, embed_scale, mult, tuple(layers), raw=tuple(raw.items()),
                    max_positions=int(raw.get("max_positions", 1 << 20)))
 
@@ -186,10 +190,11 @@ class BanelixConfig:
         d = self.width
         norm = NormSpec(kind="rmsnorm", dim=d, eps=self.eps)
         # the cache of a layer keeps the largest window of the layers that read it
-        keep = {i: L.attention.window for i, L in enumerate(self.layers) if L.type == "attention" and L.attention.kv_from is None}
+        keep = {i: L.attention.window for i, L in enumerate(self.layers) if L.attention.kv_from is None}
         for L in self.layers:
-            if L.type == "attention" and L.attention.kv_from is not None:
-                keep[L.attention.kv_from] = max(keep[L.attention.kv_from], L.attention.window)
+            if L.attention.kv_from is not None:
+                mine, theirs = L.attention.window, keep[L.attention.kv_from]
+                keep[L.attention.kv_from] = None if mine is None or theirs is None else max(mine, theirs)
         blocks, schedule = [], []
         for i, L in enumerate(self.layers):
             a = L.attention

@@ -76,7 +76,7 @@ struct FusedQkv {
 // by zero (what lies in the scratch there may be NaN).
 template <int D>
 __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const float* po_base, const float* pml_base,
-                                              int n_splits, int valid, bf16* out_rows) {
+                                              int n_splits, int valid, bf16* out_rows, int sink) {
     __shared__ int s_last;
     __syncthreads();                                   // every thread's partial results are written ...
     if (threadIdx.x == 0) {
@@ -126,6 +126,7 @@ __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const f
                     a[6] = fmaf(v[k][1].z, ws, a[6]); a[7] = fmaf(v[k][1].w, ws, a[7]);
                 }
             }
+            if (sink) L += exp2f(-M);                 // the sink's term 2^(0 - M), once for all splits
             const float inv = 1.0f / L;
             uint4 w4;
             w4.x = pack_bf16(a[0] * inv, a[1] * inv);
@@ -162,6 +163,7 @@ __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const f
             L += sm_l[r * n_splits + s] * w;
         }
         L = warp_sum(L);
+        if (sink) L += exp2f(-M);
         if (lane == 0) linv[r] = 1.0f / L;
     }
     __syncthreads();
@@ -212,7 +214,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        int tok_first, int n_heads, int n_kv, int page_size, int window, float scale_log2,
                        int chunk, int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml,
                        bf16* __restrict__ out, int out_stride, int* __restrict__ counters,
-                       int* __restrict__ err_flag, const FusedQkv fq) {
+                       int* __restrict__ err_flag, const FusedQkv fq, int sink) {
     using Plan = TdPlan<D>;
     using Layout = Swizzled128<D, 16>;
     constexpr int STAGES = Plan::STAGES;
@@ -262,7 +264,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (counters)
             merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
                              po - (size_t)split * D, pml - (size_t)split * 2, n_splits, valid,
-                             out + (size_t)t * out_stride + (size_t)h0 * D);
+                             out + (size_t)t * out_stride + (size_t)h0 * D, sink);
         return;
     }
     float2* sc = reinterpret_cast<float2*>(smem + Plan::FUSED_OFFSET);            // [rotary_dim / 2] (sine, cosine)
@@ -546,7 +548,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (counters)                                      // (its first barrier also ends the reads of red_o above)
         merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
                          po - (size_t)split * D, pml - (size_t)split * 2, n_splits, valid,
-                         out + (size_t)t * out_stride + (size_t)h0 * D);
+                         out + (size_t)t * out_stride + (size_t)h0 * D, sink);
     TL_END(TL_ATTN_DECODE);
 }
 
@@ -557,7 +559,7 @@ constexpr int COMBINE_MAX_SPLITS = 256;
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                     bf16* __restrict__ out, int out_stride, int tok_first, int n_tok, int n_heads,
-                    int n_splits, int head_dim) {
+                    int n_splits, int head_dim, int sink) {
     __shared__ float wsm[4][COMBINE_MAX_SPLITS];
     pdl_launch_dependents();
     pdl_wait();
@@ -578,6 +580,7 @@ attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict
     __syncwarp();
     float L = 0.f;
     for (int s = 0; s < n_splits; ++s) L += ml[s * 2 + 1] * wgt[s];    // ascending, same in every lane (l is written for every split)
+    if (sink) L += exp2f(-M);
     const float inv = 1.0f / L;
     bf16* orow = out + (size_t)(tok_first + ti) * out_stride + (size_t)h * head_dim;
     for (int d = lane * 2; d < head_dim; d += 64) {
@@ -600,7 +603,7 @@ template <int D, bool FUSED>
 int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const int* block_table,
                int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
                int n_kv, int page_size, int window, float scale_log2, int chunk, int n_splits, float* po, float* pml,
-               void* out, int out_stride, int* counters, int* err, const FusedQkv& fq, cudaStream_t stream) {
+               void* out, int out_stride, int* counters, int* err, const FusedQkv& fq, int sink, cudaStream_t stream) {
     using Plan = TdPlan<D>;
     constexpr int SMEM = FUSED ? Plan::TOTAL_FUSED : Plan::TOTAL;
     auto kern = attn_decode_tma_kernel<D, FUSED>;
@@ -617,7 +620,7 @@ int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int 
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), n_tok);
     launch_pdl(kern, grid, dim3(TD_THREADS), SMEM, stream, mk, mv, (const bf16*)q, q_stride, block_table,
                max_blocks, tok_entry, positions, tok_first, n_heads, n_kv, page_size, window, scale_log2, chunk,
-               n_splits, po, pml, (bf16*)out, out_stride, counters, err, fq);
+               n_splits, po, pml, (bf16*)out, out_stride, counters, err, fq, sink);
     return infero_check_launch(FUSED ? "attn_decode_tma_fused" : "attn_decode_tma");
 }
 
@@ -626,7 +629,7 @@ int decode_tma(const void* q, int q_stride, const FusedQkv& fq, void* out, int o
                const void* v_cache, int num_pages, const int* block_table, int max_blocks, const int* tok_entry,
                const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim, int page_size,
                int window, float scale, int chunk, int n_splits, void* scratch, int* counters, int n_counters,
-               cudaStream_t stream) {
+               int sink, cudaStream_t stream) {
     if (n_tok == 0) return 0;
     INFERO_REQUIRE(infero_attn_decode_tma_supported(head_dim, page_size),
                    "attn_decode_tma: head_dim %d / page_size %d not supported", head_dim, page_size);
@@ -654,7 +657,7 @@ int decode_tma(const void* q, int q_stride, const FusedQkv& fq, void* out, int o
 #define GO(D_, F_)                                                                                                   \
     rc = launch_tma<D_, F_>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,   \
                             n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, out, out_stride,       \
-                            counters, err, fq, stream)
+                            counters, err, fq, sink, stream)
     if (head_dim == 128) {
         if (fq.partial) GO(128, true); else GO(128, false);
     } else {
@@ -664,7 +667,7 @@ int decode_tma(const void* q, int q_stride, const FusedQkv& fq, void* out, int o
     if (rc || counters) return rc;                     // merged by the last CTA of every group
     const int warps = n_tok * n_heads;
     launch_pdl(attn_combine_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, (const float*)po, (const float*)pml,
-               (bf16*)out, out_stride, tok_first, n_tok, n_heads, n_splits, head_dim);
+               (bf16*)out, out_stride, tok_first, n_tok, n_heads, n_splits, head_dim, sink);
     return infero_check_launch("attn_combine");
 }
 
@@ -689,7 +692,20 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
     FusedQkv none = {};
     return decode_tma(q, q_stride, none, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
                       positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
-                      scratch, counters, n_counters, stream);
+                      scratch, counters, n_counters, 0, stream);
+}
+
+// The same with a sink: the softmax's sum has one more term exp(0) that carries no value, added where the splits of a
+// row are merged.
+int infero_attn_decode_tma_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                                const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
+                                int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
+                                void* scratch, int* counters, int n_counters, int sink, cudaStream_t stream) {
+    FusedQkv none = {};
+    return decode_tma(q, q_stride, none, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
+                      positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
+                      scratch, counters, n_counters, sink, stream);
 }
 
 // Can the kernel below finish the q/k/v product itself?  (The vector widths its loads and stores use.)
@@ -729,7 +745,7 @@ int infero_attn_decode_tma_fused(const float* partial, int splits, long long spl
     fq.sumsq_in = sumsq, fq.in_tiles = sumsq_tiles, fq.inv_d = inv_d, fq.eps = eps;
     return decode_tma(nullptr, 0, fq, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
                       positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
-                      scratch, counters, n_counters, stream);
+                      scratch, counters, n_counters, 0, stream);
 }
 
 }  // extern "C"

@@ -127,6 +127,27 @@ __global__ void head_gate_kernel(const T* __restrict__ a, int a_stride, const fl
     out[(size_t)t * out_stride + c] = from_f32<T>(v);
 }
 
+// Eight neighbouring columns a thread (they lie in one head when V is a multiple of 8): 16-byte loads and stores.
+__global__ void head_gate_vec_kernel(const bf16* __restrict__ a, int a_stride, const float* __restrict__ gate, int gate_stride,
+                                     bf16* __restrict__ out, int out_stride, int n_tokens, int H, int V, float scale) {
+    const int per_row = H * V / 8;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_tokens * per_row) return;
+    const int t = (int)(i / per_row), c = (int)(i % per_row) * 8, h = c / V;
+    float f = scale;
+    if (gate) f *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + h]));
+    const uint4 v = *reinterpret_cast<const uint4*>(a + (size_t)t * a_stride + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+        const __nv_bfloat162 p = __floats2bfloat162_rn(lo * f, hi * f);
+        r[j] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * out_stride + c) = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 }  // namespace
 
 extern "C" {
@@ -163,6 +184,12 @@ int infero_head_gate(const void* a, int a_stride, const float* gate, int gate_st
     if (n_tokens == 0) return 0;
     const long long total = (long long)n_tokens * H * V;
     const unsigned blocks = (unsigned)((total + 255) / 256);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (dtype != INFERO_F32 && V % 8 == 0 && a_stride % 8 == 0 && out_stride % 8 == 0 && al16(a) && al16(out)) {
+        head_gate_vec_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, stream>>>((const bf16*)a, a_stride, gate, gate_stride,
+                                                                                     (bf16*)out, out_stride, n_tokens, H, V, scale);
+        return infero_check_launch("head_gate");
+    }
     if (dtype == INFERO_F32)
         head_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)a, a_stride, gate, gate_stride, (float*)out,
                                                              out_stride, n_tokens, H, V, scale);

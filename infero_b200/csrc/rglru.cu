@@ -19,19 +19,19 @@
 // engine's tensor-core product block by block) and rglru_scan.  The gate products are laid out block by block:
 // gates[t, b, 0, :] the products of Ra[b], gates[t, b, 1, :] those of Ri[b] (each C / blocks wide).
 //
-// rglru_scan: a block takes 32 channels of one request; its warps cut the request's new tokens into as many segments.
-// S_t = a_t S_(t-1) + b_t is linear in S, so each warp first runs its segment from S = 0 and leaves (product of a, end
-// state); the segments before a warp's own are then folded in order to give its start state, and a second pass writes
-// the outputs.  Single tokens and short portions run as one segment, in order.  The last warp writes the new S, the
-// first the new tail.
+// With the tensor-core product the bf16 copy of u and the gates are laid out block-major ([blocks, rows, ...], rows padded
+// to the product's tile) so that one grouped product does all blocks.  rglru_scan is described at the kernel.
 #include "common.cuh"
 
 namespace {
 
-__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+// (a correctly rounded reciprocal in place of the division: a few instructions instead of a dozen)
+__device__ __forceinline__ float sigmoidf_(float z) { return __frcp_rn(1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// 0.5 z (1 + tanh w) = z / (1 + exp(-2 w)), w = sqrt(2 / pi) (z + 0.044715 z^3)
 __device__ __forceinline__ float gelu_tanhf_(float z) {
-    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float w = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    return z * __frcp_rn(1.0f + expf(-2.0f * w));
 }
 
 constexpr int MAX_TAPS = 16;
@@ -40,7 +40,7 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, int proj_strid
                                   const float* __restrict__ conv_b, int taps, const float* __restrict__ state,
                                   const int* __restrict__ tok_entry, const int* __restrict__ entry_q_start,
                                   const int* __restrict__ entry_slot, float* __restrict__ u, bf16* __restrict__ u16,
-                                  int n_tokens, int C) {
+                                  int bs, long long u16_blk, int n_tokens, int C) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)n_tokens * C) return;
     const int t = (int)(idx / C), c = (int)(idx % C);
@@ -56,7 +56,7 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, int proj_strid
         acc = fmaf(conv_w[(size_t)c * taps + j], xv, acc);
     }
     u[(size_t)t * C + c] = acc;
-    if (u16) u16[(size_t)t * C + c] = __float2bfloat16_rn(acc);
+    if (u16) u16[(size_t)(c / bs) * u16_blk + (size_t)t * bs + (c % bs)] = __float2bfloat16_rn(acc);
 }
 
 constexpr int BM = 64, BN = 64, BK = 16;
@@ -113,70 +113,102 @@ rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wg, float
     }
 }
 
-constexpr int MAX_SEGS = 16;
+constexpr int SEG = 16;              // tokens of a segment
 
-template <typename T>
-__global__ void __launch_bounds__(32 * MAX_SEGS)
+// A warp holds CH channels times 32 / CH segments; a block of W warps W * 32 / CH segments of SEG tokens: a stretch.  A
+// request's new tokens are worked through stretch by stretch.  S_t = a_t S_(t-1) + b_t is linear in S, so every thread
+// first runs its segment from S = 0, keeps (a_t, b_t) in shared memory and leaves (product of a, end value); the segments
+// before a thread's own are folded in order from the stretch's start state, and the second pass runs the segment again
+// from there, from the kept pairs, and writes the outputs.  The thread that ran the stretch's last segment hands its
+// end state to the next stretch; the one that ran the request's last token writes the new S.  How a request is cut
+// depends on its own length alone (segments of SEG tokens from its first new token), and the fold is in order, so
+// neither the width of a block nor what else is in the step changes a bit of the result.
+// gates: the products of token t, block b at gates + t * g_tok + b * g_blk: Ra's bs, then Ri's bs.
+template <typename T, int CH>
+__global__ void __launch_bounds__(512)
 rglru_scan_kernel(const float* __restrict__ proj, int proj_stride, int y_off, int x_off, const float* __restrict__ u,
-                  const float* __restrict__ gates, const float* __restrict__ ra_b, const float* __restrict__ ri_b,
-                  const float* __restrict__ lam, float slope, int taps, float* __restrict__ state,
-                  const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
+                  const float* __restrict__ gates, long long g_tok, long long g_blk, const float* __restrict__ ra_b,
+                  const float* __restrict__ ri_b, const float* __restrict__ lam, float slope, int taps,
+                  float* __restrict__ state, const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                   const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride, int C, int bs, float scale) {
-    __shared__ float As[MAX_SEGS][32], Bs[MAX_SEGS][32];
-    const int tx = threadIdx.x, w = threadIdx.y, segs = blockDim.y;
-    const int c = blockIdx.x * 32 + tx;
+    constexpr int SUB = 32 / CH;
+    extern __shared__ float2 scan_smem[];
+    const int threads = blockDim.x, tid = threadIdx.x;
+    const int nseg = (threads / 32) * SUB;
+    float2* ab = scan_smem;                                  // [SEG][threads]
+    float2* fold = scan_smem + (size_t)SEG * threads;        // [nseg][CH]
+    float* carry = reinterpret_cast<float*>(fold + (size_t)nseg * CH);   // [CH]
+    const int lane = tid & 31, ch = lane % CH, segi = (tid >> 5) * SUB + lane / CH;
+    const int c = blockIdx.x * CH + ch;
     const bool live = c < C;
     const int e = blockIdx.y;
     const int t0 = entry_q_start[e], n = entry_q_len[e];
     if (n <= 0) return;                                      // (the whole block: n is the request's)
     float* st = state + (size_t)entry_slot[e] * taps * C;
-    // segments of about 32 tokens, as many as the request's own portion asks for (what else is in the step does not
-    // change how a request is cut); warps beyond that have nothing to do but pass the state on
-    const int eff = min(segs, max(1, (n + 31) / 32));
-    const int seg = (n + eff - 1) / eff;
-    const int k0 = min(n, w * seg), k1 = min(n, k0 + seg);
-    float S = 0.f, sp = 0.f, ba = 0.f, bi = 0.f;
-    size_t gcol = 0;
+    float sp = 0.f, ba = 0.f, bi = 0.f;
+    const float* gp = gates;
     if (live) {
-        S = st[(size_t)(taps - 1) * C + c];
         sp = slope * softplusf_(lam[c]);
         ba = ra_b[c], bi = ri_b[c];
-        gcol = (size_t)(c / bs) * 2 * bs + (c % bs);
+        gp = gates + (size_t)(c / bs) * g_blk + (c % bs);
+        if (segi == 0) carry[ch] = st[(size_t)(taps - 1) * C + c];
     }
-    // a_t and b_t of token k: S_t = a_t S_(t-1) + b_t
-    auto step = [&](int k, float& a, float& b) {
-        const size_t t = (size_t)(t0 + k);
-        const float uv = u[t * C + c];
-        const float r = sigmoidf_(gates[t * 2 * C + gcol] + ba);
-        const float i = sigmoidf_(gates[t * 2 * C + gcol + bs] + bi);
-        const float log_a = -sp * r;
-        a = expf(log_a);
-        b = sqrtf(-expm1f(2.0f * log_a)) * (i * uv);
-    };
-    if (segs > 1) {
+    for (int base = 0; base < n; base += nseg * SEG) {
+        const int k0 = min(n, base + segi * SEG), k1 = min(n, k0 + SEG);
         float A = 1.f, B = 0.f;
-        if (live)
-            for (int k = k0; k < k1; ++k) {
-                float a, b;
-                step(k, a, b);
-                B = fmaf(a, B, b);
-                A *= a;
+        if (live && k0 < k1) {
+            // all of the segment's loads first, so that they are in flight together
+            float uv[SEG], gr[SEG], gi[SEG];
+#pragma unroll
+            for (int j = 0; j < SEG; ++j) {
+                const size_t t = (size_t)(t0 + min(k0 + j, k1 - 1));
+                uv[j] = u[t * C + c];
+                gr[j] = gp[t * g_tok];
+                gi[j] = gp[t * g_tok + bs];
             }
-        As[w][tx] = A, Bs[w][tx] = B;
+#pragma unroll
+            for (int j = 0; j < SEG; ++j) {
+                if (k0 + j < k1) {
+                    const float r = sigmoidf_(gr[j] + ba);
+                    const float i = sigmoidf_(gi[j] + bi);
+                    // a = exp(log a) = 1 + e with e = expm1(log a); 1 - a^2 = -e (2 + e) keeps its digits where a is close to 1
+                    const float e = expm1f(-sp * r);
+                    const float a = 1.0f + e;
+                    const float b = sqrtf(-e * (2.0f + e)) * (i * uv[j]);
+                    ab[(size_t)j * threads + tid] = make_float2(a, b);
+                    B = fmaf(a, B, b);
+                    A *= a;
+                }
+            }
+        }
+        fold[segi * CH + ch] = make_float2(A, B);
         __syncthreads();
-        for (int j = 0; j < w; ++j) S = fmaf(As[j][tx], S, Bs[j][tx]);
+        float S = carry[ch];
+        for (int j = 0; j < segi; ++j) {
+            const float2 f = fold[j * CH + ch];
+            S = fmaf(f.x, S, f.y);
+        }
+        __syncthreads();                                     // (every thread has read the stretch's start state)
+        if (live) {
+            if (k0 < k1) {
+                float yv[SEG];
+#pragma unroll
+                for (int j = 0; j < SEG; ++j) yv[j] = proj[(size_t)(t0 + min(k0 + j, k1 - 1)) * proj_stride + y_off + c];
+#pragma unroll
+                for (int j = 0; j < SEG; ++j) {
+                    if (k0 + j < k1) {
+                        const float2 f = ab[(size_t)j * threads + tid];
+                        S = fmaf(f.x, S, f.y);
+                        out[(size_t)(t0 + k0 + j) * out_stride + c] = from_f32<T>(S * gelu_tanhf_(yv[j]) * scale);
+                    }
+                }
+            }
+            if (k0 < n && k1 == n) st[(size_t)(taps - 1) * C + c] = S;          // ran the request's last token
+            else if (segi == nseg - 1) carry[ch] = S;                              // ran the stretch's last segment
+        }
+        __syncthreads();
     }
-    if (!live) return;
-    for (int k = k0; k < k1; ++k) {
-        float a, b;
-        step(k, a, b);
-        S = fmaf(a, S, b);
-        const size_t t = (size_t)(t0 + k);
-        const float y = gelu_tanhf_(proj[t * proj_stride + y_off + c]);
-        out[t * out_stride + c] = from_f32<T>(S * y * scale);
-    }
-    if (w == segs - 1) st[(size_t)(taps - 1) * C + c] = S;      // (an empty last segment holds the folded state)
-    if (w == 0) {
+    if (live && segi == 0) {
         // the new tail: the last taps-1 inputs of (old tail, this portion), oldest first
         float keep[MAX_TAPS];
         for (int j = 0; j < taps - 1; ++j) {
@@ -192,14 +224,19 @@ rglru_scan_kernel(const float* __restrict__ proj, int proj_stride, int y_off, in
 
 extern "C" {
 
+// u_bf16 (optional): a bf16 copy of u laid out block by block, [blocks, rows_per_block, C / blocks], for a grouped
+// tensor-core product of the gates.
 int infero_rglru_conv(const float* proj, int proj_stride, int x_off, const float* conv_w, const float* conv_b, int taps,
                       const float* state, const int* tok_entry, const int* entry_q_start, const int* entry_slot, float* u,
-                      void* u_bf16, int n_tokens, int C, cudaStream_t stream) {
+                      void* u_bf16, int blocks, long long rows_per_block, int n_tokens, int C, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "rglru: %d taps outside 1..%d", taps, MAX_TAPS);
+    INFERO_REQUIRE(!u_bf16 || (blocks >= 1 && C % blocks == 0 && rows_per_block >= n_tokens), "rglru: bad layout of the bf16 copy");
     const long long total = (long long)n_tokens * C;
+    const int bs = u_bf16 ? C / blocks : C;
     rglru_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(proj, proj_stride, x_off, conv_w, conv_b, taps, state,
-                                                                          tok_entry, entry_q_start, entry_slot, u, (bf16*)u_bf16, n_tokens, C);
+                                                                          tok_entry, entry_q_start, entry_slot, u, (bf16*)u_bf16,
+                                                                          bs, rows_per_block * bs, n_tokens, C);
     return infero_check_launch("rglru_conv");
 }
 
@@ -217,26 +254,43 @@ int infero_rglru_gates(const float* u, const void* wg, int w_dtype, float* out, 
     return infero_check_launch("rglru_gates");
 }
 
+// gates: token t's products for block b start at gates + t * g_tok + b * g_blk (floats): Ra[b]'s, then Ri[b]'s.
+// (token-major from rglru_gates: g_tok = 2 C, g_blk = 2 C / blocks; block-major from a grouped product over
+// [blocks, rows, C / blocks]: g_tok = 2 C / blocks, g_blk = rows * 2 C / blocks.)
 int infero_rglru_scan(const float* proj, int proj_stride, int y_off, int x_off, const float* u, const float* gates,
-                      const float* ra_b, const float* ri_b, const float* lam, float slope, int taps, float* state,
-                      const int* entry_q_start, const int* entry_q_len, const int* entry_slot, void* out, int out_stride,
-                      int out_dtype, int n_entries, int C, int blocks, int max_q_len, float scale, cudaStream_t stream) {
+                      long long g_tok, long long g_blk, const float* ra_b, const float* ri_b, const float* lam, float slope,
+                      int taps, float* state, const int* entry_q_start, const int* entry_q_len, const int* entry_slot,
+                      void* out, int out_stride, int out_dtype, int n_entries, int C, int blocks, int max_q_len, float scale,
+                      cudaStream_t stream) {
     if (n_entries == 0) return 0;
     INFERO_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "rglru: %d taps outside 1..%d", taps, MAX_TAPS);
     INFERO_REQUIRE(n_entries <= 65535, "rglru: %d requests in a step", n_entries);
     INFERO_REQUIRE(blocks >= 1 && C % blocks == 0, "rglru: %d channels in %d blocks", C, blocks);
-    // enough warps for the longest portion of the step; each request uses as many as its own portion asks for
-    int segs = (max_q_len + 31) / 32;
-    segs = segs < 1 ? 1 : segs > MAX_SEGS ? MAX_SEGS : segs;
-    dim3 grid((C + 31) / 32, n_entries), block(32, segs);
-    if (out_dtype == INFERO_F32)
-        rglru_scan_kernel<float><<<grid, block, 0, stream>>>(proj, proj_stride, y_off, x_off, u, gates, ra_b, ri_b, lam, slope, taps,
-                                                             state, entry_q_start, entry_q_len, entry_slot, (float*)out,
-                                                             out_stride, C, C / blocks, scale);
-    else
-        rglru_scan_kernel<bf16><<<grid, block, 0, stream>>>(proj, proj_stride, y_off, x_off, u, gates, ra_b, ri_b, lam, slope, taps,
-                                                            state, entry_q_start, entry_q_len, entry_slot, (bf16*)out,
-                                                            out_stride, C, C / blocks, scale);
+    const int bs = C / blocks;
+    // steps of short portions: a warp of 32 channels per segment, as many warps as the longest portion has segments (two
+    // at most); steps with long portions: 8 channels times 4 segments a warp, 16 warps
+    const bool wide = max_q_len > 2 * SEG;
+    const int ch = wide ? 8 : 32;
+    const int warps = wide ? 16 : (max_q_len > SEG ? 2 : 1);
+    const int threads = 32 * warps, nseg = warps * (32 / ch);
+    const size_t smem = (size_t)SEG * threads * sizeof(float2) + (size_t)nseg * ch * sizeof(float2) + ch * sizeof(float);
+    dim3 grid((C + ch - 1) / ch, n_entries);
+#define LAUNCH(T, CH)                                                                                                    \
+    do {                                                                                                                 \
+        auto k = rglru_scan_kernel<T, CH>;                                                                               \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        k<<<grid, threads, smem, stream>>>(proj, proj_stride, y_off, x_off, u, gates, g_tok, g_blk, ra_b, ri_b, lam,      \
+                                           slope, taps, state, entry_q_start, entry_q_len, entry_slot, (T*)out,          \
+                                           out_stride, C, bs, scale);                                                    \
+    } while (0)
+    if (out_dtype == INFERO_F32) {
+        if (wide) LAUNCH(float, 8);
+        else LAUNCH(float, 32);
+    } else {
+        if (wide) LAUNCH(bf16, 8);
+        else LAUNCH(bf16, 32);
+    }
+#undef LAUNCH
     return infero_check_launch("rglru_scan");
 }
 

@@ -50,19 +50,18 @@ def _arrival_counters(device) -> torch.Tensor:
 def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int, n_tok: int, n_heads: int,
            n_kv: int, head_dim: int, page_size: int, window: Optional[int], scale: float, chunk: int,
            n_splits: int, sink: bool = False) -> None:
-    """``sink`` (one more term exp(0) in the softmax's sum) is added where the splits are merged; the kernel that merges
-    inside the attention kernel has no such term, so a step with a sink takes the two-kernel form."""
+    """``sink``: one more term exp(0) in the softmax's sum, added where the splits of a row are merged."""
     need = int(lib_scratch(n_tok, n_heads, head_dim, n_splits))
     scratch = torch.empty(need // 4, dtype=torch.float32, device=q.device)
-    if not sink and lib().infero_attn_decode_tma_supported(c_int(head_dim), c_int(page_size)) and k_cache.is_contiguous() \
+    if lib().infero_attn_decode_tma_supported(c_int(head_dim), c_int(page_size)) and k_cache.is_contiguous() \
             and v_cache.is_contiguous():
-        _check(lib().infero_attn_decode_tma(
+        _check(lib().infero_attn_decode_tma_sink(
             _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
             c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
             _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")), c_int(tok_first), c_int(n_tok),
             c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale),
             c_int(chunk), c_int(n_splits), _ptr(scratch), _ptr(_arrival_counters(q.device)), c_int(N_COUNTERS),
-            _stream()))
+            c_int(1 if sink else 0), _stream()))
         return
     _check(lib().infero_attn_decode_sink(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
                                          _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),

@@ -383,8 +383,8 @@ def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv
     ``conv_w`` float32 [C, taps]; ``w_gates`` [blocks, 2 C/blocks, C/blocks] (float32 or bf16): per block the rows of Ra,
     then those of Ri; ``state`` float32 [slots, taps, C] (rows 0..taps-2 the convolution's last inputs, row taps-1 the
     recurrent state); ``out`` [T, C] (a column slice allowed) receives S * gelu_tanh(y) * scale.  ``max_q_len``: the
-    longest portion of the step.  ``tensor_cores``: the gate products of a long bf16 step run on the tensor-core product,
-    block by block, from u rounded to bf16 (32-bit sums); otherwise they are 32-bit throughout."""
+    longest portion of the step.  ``tensor_cores``: the gate products of a long bf16 step run as one grouped
+    tensor-core product over all blocks, from u rounded to bf16 (32-bit sums); otherwise they are 32-bit throughout."""
     T = proj.shape[0]
     C, taps = conv_w.shape
     blocks, two_bs, bs = w_gates.shape
@@ -393,26 +393,31 @@ def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv
     assert blocks * bs == C and two_bs == 2 * bs and w_gates.is_contiguous()
     _f32(conv_w, "conv_w"), _f32(conv_b, "conv_b"), _f32(ra_b, "ra_b"), _f32(ri_b, "ri_b"), _f32(lam, "lam")
     u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
-    gates = torch.empty((T, 2 * C), dtype=torch.float32, device=proj.device)
-    use_tc = False
-    if tensor_cores and T > 256 and w_gates.dtype == torch.bfloat16 and bs % 8 == 0:
-        from . import tc_gemm
-        u16 = torch.empty((T, C), dtype=torch.bfloat16, device=proj.device)
-        use_tc = all(tc_gemm.supported(u16[:, b * bs:(b + 1) * bs], w_gates[b], gates[:, 2 * b * bs:2 * (b + 1) * bs])
-                     for b in (0, blocks - 1))
     L = lib()
+    u16 = None
+    rows = -(-T // 128) * 128
+    if tensor_cores and T > 256 and w_gates.dtype == torch.bfloat16:
+        from . import latent_attention as LA
+        u16 = torch.empty((blocks, rows, bs), dtype=torch.bfloat16, device=proj.device)
+        if not LA.grouped_ok(u16, w_gates):
+            u16 = None
     _check(L.infero_rglru_conv(_ptr(proj), c_int(proj.stride(0)), c_int(x_off), _ptr(conv_w), _ptr(conv_b), c_int(taps),
                                _ptr(state), _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(entry_q_start, "entry_q_start")),
-                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(u), _ptr(u16 if use_tc else None), c_int(T), c_int(C),
-                               _stream()))
-    if use_tc:
-        for b in range(blocks):
-            tc_gemm.gemm(u16[:, b * bs:(b + 1) * bs], w_gates[b], None, gates[:, 2 * b * bs:2 * (b + 1) * bs])
+                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(u), _ptr(u16), c_int(blocks), c_longlong(rows), c_int(T),
+                               c_int(C), _stream()))
+    if u16 is not None:
+        # one grouped product over all blocks: [blocks, rows, bs] x [blocks, 2 bs, bs]^T -> [blocks, rows, 2 bs]
+        gates = torch.empty((blocks, rows, 2 * bs), dtype=torch.float32, device=proj.device)
+        LA.per_head_product(u16, w_gates, gates, T)
+        g_tok, g_blk = 2 * bs, rows * 2 * bs
     else:
+        gates = torch.empty((T, 2 * C), dtype=torch.float32, device=proj.device)
         _check(L.infero_rglru_gates(_ptr(u), _ptr(w_gates), c_int(_dt(w_gates)), _ptr(gates), c_int(T), c_int(C), c_int(blocks),
                                     _stream()))
-    _check(L.infero_rglru_scan(_ptr(proj), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(u), _ptr(gates), _ptr(ra_b),
-                               _ptr(ri_b), _ptr(lam), c_float(slope), c_int(taps), _ptr(state),
-                               _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
-                               _ptr(_i32(entry_slot, "entry_slot")), _ptr(out), c_int(out.stride(0)), c_int(_dt(out)),
+        g_tok, g_blk = 2 * C, 2 * bs
+    _check(L.infero_rglru_scan(_ptr(proj), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(u), _ptr(gates),
+                               c_longlong(g_tok), c_longlong(g_blk), _ptr(ra_b), _ptr(ri_b), _ptr(lam), c_float(slope),
+                               c_int(taps), _ptr(state), _ptr(_i32(entry_q_start, "entry_q_start")),
+                               _ptr(_i32(entry_q_len, "entry_q_len")), _ptr(_i32(entry_slot, "entry_slot")), _ptr(out),
+                               c_int(out.stride(0)), c_int(_dt(out)),
                                c_int(n_entries), c_int(C), c_int(blocks), c_int(max(1, int(max_q_len))), c_float(scale), _stream()))

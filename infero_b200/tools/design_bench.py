@@ -1,7 +1,7 @@
-"""Vufizen or Gositar beside Qwen2 at equal layer sizes: whole prompt steps and decode steps, and the designs' own
+"""Vufizen, Gositar or Banelix beside Qwen2 at equal layer sizes: whole prompt steps and decode steps, and the designs' own
 kernels one by one against their rooflines.
 
-    python -m infero_b200.tools.design_bench [--design vufizen|gositar] [--sizes s,m] [--prompt 2048] [--context 2048]
+    python -m infero_b200.tools.design_bench [--design vufizen|gositar|banelix] [--sizes s,m] [--prompt 2048] [--context 2048]
                                              [--batch 8] [--layers 8]
 
 (also ``bench.py --designs``).  Random weights made on the device, bf16.  Per size two models of the same width
@@ -13,6 +13,10 @@ timed alone the same way.  One JSON line at the end.
 Gositar (``--design gositar``): latent attention in every layer (both mixer types alternating), dense squared-relu and
 group-routed expert feed-forwards alternating, four residual streams; beside Qwen2 with the same head count, heads of
 128, a quarter as many kv heads, and a feed-forward as wide as what one token uses on average.
+
+Banelix (``--design banelix``): parallel layers (causal attention whose values are its keys beside a gated linear
+recurrence) and windowed attention layers with a sink alternating, every second attention layer reading the keys and
+values of the one before it; beside Qwen2 with the same width, head counts, heads of 128 and feed-forward.
 """
 from __future__ import annotations
 
@@ -60,6 +64,39 @@ def qwen2_beside_gositar(z, layers):
     return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers,
             "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": max(1, z["heads"] // 4),
             "head_dim": 128, "intermediate_size": -(-used // 64) * 64, "vocab_size": z["vocab"],
+            "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+
+
+BANELIX_SIZES = {
+    "t": dict(width=256, heads=4, kv=2, dim=64, window=48, rec=256, blocks=4, taps=4, ff=512, vocab=1000),            # for tests
+    "s": dict(width=1024, heads=8, kv=2, dim=128, window=1024, rec=1024, blocks=8, taps=4, ff=4096, vocab=32000),
+    "m": dict(width=2048, heads=16, kv=4, dim=128, window=1024, rec=2048, blocks=16, taps=4, ff=6144, vocab=32000),
+    "l": dict(width=4096, heads=32, kv=8, dim=128, window=1024, rec=4096, blocks=32, taps=4, ff=11008, vocab=32000),
+}
+
+
+def banelix_config(z, layers):
+    D = z["dim"]
+    left = {"heads": max(1, z["heads"] // 2), "kv_heads": max(1, z["kv"] // 2), "dim": D, "vdim": D, "scale": D ** -0.5,
+            "rot": {"base": 500000.0, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    par = {"left": left, "right": {"width": z["rec"], "blocks": z["blocks"], "conv": z["taps"]}, "left_scale": 0.7, "right_scale": 0.7}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": z["window"]},
+           "rot": {"base": 10000.0, "dims": D, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "parallel", "mixer": par, "mlp": mlp})
+        else:
+            out.append({"type": "attention", "mixer": dict(att, kv_from=i - 2) if i % 4 == 3 else att, "mlp": mlp})
+    return {"architecture": "Banelix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.5, "layers": out}
+
+
+def qwen2_beside_banelix(z, layers):
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers,
+            "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+            "head_dim": z["dim"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
             "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
 
 
@@ -436,9 +473,108 @@ def time_gositar_kernels(z, T, context, batch, timer, peaks):
     return rows
 
 
+def time_banelix_kernels(z, T, context, batch, timer, peaks):
+    """Banelix's kernels alone, each beside the kernel of the built-in decoder that does the like job."""
+    import numpy as np
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.kernels import attention as A, layer_ops as L
+    dev, bf = "cuda:0", torch.bfloat16
+    d, H, G, D, W, C, nb, taps = z["width"], z["heads"], z["kv"], z["dim"], z["window"], z["rec"], z["blocks"], z["taps"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s, dtype=bf, k=1.0: (torch.randn(s, generator=g, device=dev) * k).to(dtype)     # noqa: E731
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev)                 # noqa: E731
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    rows = {}
+
+    def note(name, ms, bytes_=0.0, flops=0.0, **more):
+        r = {"us": round(ms * 1e3, 1)}
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["hbm_frac"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["tensor_frac"] = round(flops / ms / 1e9 / tfl, 3)
+        r.update(more)
+        rows[name] = r
+
+    def batch_ctx(q_lens, pos0, ps=16):
+        E_ = len(q_lens)
+        per = [-(-(p + n) // ps) for p, n in zip(pos0, q_lens)]
+        table = torch.full((E_, max(per)), -1, dtype=torch.int32)
+        at = 0
+        for e, n in enumerate(per):
+            table[e, :n] = torch.arange(at, at + n, dtype=torch.int32)
+            at += n
+        qs = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+        ctx = types.SimpleNamespace(
+            n_entries=E_, n_tokens=int(sum(q_lens)), h_q_len=np.asarray(q_lens, dtype=np.int32), h_pos0=np.asarray(pos0, dtype=np.int32),
+            tok_entry=i32(np.repeat(np.arange(E_), q_lens)), positions=i32(np.concatenate([p + np.arange(n) for p, n in zip(pos0, q_lens)])),
+            entry_q_start=i32(qs), entry_q_len=i32(q_lens), entry_pos0=i32(pos0), entry_slot=i32(np.arange(E_)), kv_bound=None)
+        return ctx, table.to(dev), at
+
+    for label, q_lens, pos0 in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx, table, pages = batch_ctx(q_lens, pos0)
+        n = ctx.n_tokens
+        # ---- attention: a window and a sink beside all keys and none -----------------------------------------------
+        kc, vc = rnd(pages, G, 16, D), rnd(pages, G, 16, D)
+        q, out = rnd(n, H * D), torch.empty(n, H * D, dtype=bf, device=dev)
+        w = min(W, T if label == "prefill" else context)
+        pairs_all = T * T / 2 if label == "prefill" else batch * context
+        pairs_win = (T * w - w * w / 2) if label == "prefill" else batch * w
+        keys_all = T if label == "prefill" else batch * context
+        keys_win = T if label == "prefill" else batch * w
+        for name, window, sink, pairs, keys in (("window_sink_attention", W, True, pairs_win, keys_win),
+                                                ("gqa_attention", None, False, pairs_all, keys_all)):
+            ms = timer(lambda: A.attention_any(q, out, kc, vc, table, ctx.tok_entry, ctx.positions, H, G, D, 16, window, D ** -0.5,
+                                               ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0, sink=sink))
+            note(f"{name}_{label}", ms, 2.0 * G * 2 * D * keys + 4.0 * n * H * D, 2.0 * H * 2 * D * pairs)
+        # ---- from the input product to queries and the cache: both norms beside rotary + cache append ---------------------
+        width = (H + 2 * G) * D
+        proj = rnd(n, width, dtype=torch.float32)
+        qo = torch.empty(n, H * D, dtype=bf, device=dev)
+        fr = torch.rand(D // 2, device=dev, dtype=torch.float64)
+        qw, kw = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
+        ms = timer(lambda: L.qk_prepare(proj, 0, H * D, (H + G) * D, 1, qw, kw, 1e-5, fr, 1.1, ctx.positions, ctx.tok_entry, table,
+                                        16, qo, kc, vc, H, G, D, D))
+        note(f"qk_prepare_projection_norm_{label}", ms, n * width * (4.0 + 2.0))
+        ms = timer(lambda: L.qk_prepare(proj, 0, H * D, -1, 2, None, None, 1e-5, fr, 1.0, ctx.positions, ctx.tok_entry, table,
+                                        16, qo, kc, vc, H, G, D, D))
+        note(f"qk_prepare_head_norm_{label}", ms, n * (H + G) * D * 4.0 + n * (H + 2 * G) * D * 2.0)
+        qkv = rnd(n, width)
+        inv = torch.rand(D // 2, device=dev)
+        ms = timer(lambda: K.rope_cache(qkv, ctx.positions, ctx.tok_entry, table, inv, kc, vc, H, G, D, 16))
+        note(f"rope_cache_{label}", ms, n * width * 2 * 2)
+        # ---- the gate per head ---------------------------------------------------------------------------------------
+        gate = rnd(n, H, dtype=torch.float32)
+        ms = timer(lambda: L.head_gate(out, gate, out, H, D, 0.7))
+        note(f"head_gate_{label}", ms, n * H * D * 4.0 + n * H * 4.0)
+        # ---- the recurrence: convolution, gate products and scan ------------------------------------------------------
+        rctx, _, _ = batch_ctx(q_lens, [0] * len(q_lens))
+        bs = C // nb
+        yx = rnd(n, 2 * C, dtype=torch.float32)
+        cw, cb = rnd(C, taps, dtype=torch.float32, k=0.3), rnd(C, dtype=torch.float32, k=0.1)
+        wg = rnd(nb, 2 * bs, bs, k=bs ** -0.5)
+        rb, ib, lam = rnd(C, dtype=torch.float32, k=0.1), rnd(C, dtype=torch.float32, k=0.1), rnd(C, dtype=torch.float32)
+        state = torch.zeros(len(q_lens), taps, C, device=dev)
+        ro = torch.empty(n, C, dtype=bf, device=dev)
+        ms = timer(lambda: L.rglru(yx, 0, C, cw, cb, wg, rb, ib, lam, 8.0, state, rctx.tok_entry, rctx.entry_q_start, rctx.entry_q_len,
+                                   rctx.entry_slot, len(q_lens), ro, 0.7, max_q_len=max(q_lens), tensor_cores=True))
+        least = n * C * (8.0 + 2.0) + 2.0 * wg.numel() + 8.0 * len(q_lens) * taps * C
+        moved = least + n * C * (4.0 + 2.0 + 4.0 + 8.0 + 8.0 + 4.0)           # u written and read twice (+ bf16), gates written and read
+        note(f"rglru_{label}", ms, least, 2.0 * n * 2 * C * bs, gb_s_with_intermediates=round(moved / ms / 1e6, 1),
+             hbm_frac_with_intermediates=round(moved / ms / 1e6 / hbm, 3))
+        # ---- add + RMSNorm with the sublayer's result times a constant (the same kernel as without) -----------------------
+        x, yv = rnd(n, d, dtype=torch.float32), rnd(n, d, dtype=torch.float32)
+        nw, hb = torch.ones(d, device=dev), torch.empty(n, d, dtype=bf, device=dev)
+        ms = timer(lambda: K.add_rmsnorm(x, yv, nw, 1e-5, hb, delta_scale=0.5))
+        note(f"add_rmsnorm_scaled_{label}", ms, n * d * (4 + 4 + 4 + 2))
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="design_bench")
-    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar"])
+    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar", "banelix"])
     ap.add_argument("--sizes", default="s,m")
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--context", type=int, default=2048)
@@ -458,8 +594,9 @@ def main(argv=None) -> int:
     except (OSError, KeyError, ValueError):
         pass
     timer = _Timer()
-    gositar = args.design == "gositar"
-    sizes, design_cfg, beside_cfg = (GOSITAR_SIZES, gositar_config, qwen2_beside_gositar) if gositar else (SIZES, vufizen_config, qwen2_config)
+    sizes, design_cfg, beside_cfg, each = {"vufizen": (SIZES, vufizen_config, qwen2_config, time_kernels),
+                                           "gositar": (GOSITAR_SIZES, gositar_config, qwen2_beside_gositar, time_gositar_kernels),
+                                           "banelix": (BANELIX_SIZES, banelix_config, qwen2_beside_banelix, time_banelix_kernels)}[args.design]
     out = {"bench": "designs", "design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.prompt, "context": args.context,
            "batch": args.batch, "layers": args.layers, "peaks": peaks, "sizes": {}}
     for name in [s for s in args.sizes.split(",") if s]:
@@ -469,7 +606,6 @@ def main(argv=None) -> int:
                               "qwen2": time_model(beside_cfg(z, args.layers), args.prompt, args.context, args.batch, timer)}
         print(f"[design_bench] {name}: {json.dumps(out['sizes'][name])}", file=sys.stderr, flush=True)
     if args.kernels_at:
-        each = time_gositar_kernels if gositar else time_kernels
         out["kernels"] = {"size": args.kernels_at,
                           "rows": each(sizes[args.kernels_at], args.prompt, args.context, args.batch, timer, peaks)}
     print(json.dumps(out))

@@ -77,15 +77,11 @@ def _bad(edit):
     lambda r: r["layers"][0]["mixer"].update(heads=3),
     lambda r: r["layers"][0]["mixer"]["rot"].update(dims=7),
     lambda r: r["layers"][0]["mixer"]["rot"].update(dims=66),
-    lambda r: r["layers"][0]["mixer"].pop("mask"),
     lambda r: r["layers"][2]["mixer"].update(kv_from=2),
-    lambda r: r["layers"][2]["mixer"].update(kv_from=1),
     lambda r: r["layers"][2]["mixer"].update(kv_heads=1),
-    lambda r: r["layers"][2]["mixer"]["rot"].update(base=7.0),
     lambda r: r["layers"][1]["mixer"]["right"].update(blocks=3),
     lambda r: r["layers"][1]["mixer"]["right"].update(conv=0),
     lambda r: r["layers"][1]["mixer"]["left"].update(vdim=32),
-    lambda r: r["layers"][1]["mixer"].pop("left_scale"),
     lambda r: r["layers"][1]["mlp"].update(kind="moe"),
     lambda r: r.update(vocab=0),
     lambda r: r["norm"].pop("eps"),
@@ -96,7 +92,24 @@ def test_refusals(edit):
         BanelixConfig.from_dict(_bad(edit))
 
 
-@pytest.mark.parametrize("dims,base,sc", [(32, 250000.0, (8.0, 1.0, 4.0, 1024)), (16, 900.0, (4.0, 1.0, 3.0, 48)),
+def test_what_a_config_leaves_out_does_not_exist():
+    raw = copy.deepcopy(CONFIGS["A"])
+    raw["layers"][0]["mixer"].pop("mask")                 # no mask: all earlier tokens
+    raw["layers"][1]["mixer"].pop("left_scale")           # a scale of one
+    raw["layers"][3]["mixer"]["left"].pop("rot")          # no rotation
+    raw["layers"][2]["mixer"]["rot"].update(base=7.0)     # the reader's own queries turn as its own table says
+    cfg = BanelixConfig.from_dict(raw)
+    assert cfg.layers[0].attention.window is None and cfg.layers[1].left_scale == 1.0 and cfg.layers[3].attention.rot.dims == 0
+    spec = cfg.to_model_spec()
+    assert spec.blocks[0].mixer.window is None and spec.blocks[0].mixer.keep_window is None      # the borrowed cache keeps all
+    assert spec.blocks[2].mixer.window == 41 and spec.blocks[3].mixer.branches[0].position is None
+    raw = copy.deepcopy(CONFIGS["A"])
+    raw["layers"][2]["mixer"].update(kv_from=1, heads=4, kv_heads=2)     # the keys and values of a parallel layer's attention
+    spec = BanelixConfig.from_dict(raw).to_model_spec()
+    assert spec.schedule[2].cache == 1 and not spec.schedule[2].write_cache
+
+
+@pytest.mark.parametrize("dims,base,sc", [(32, 120000.0, (6.0, 1.0, 4.0, 2048)), (16, 900.0, (4.0, 1.0, 3.0, 48)),
                                           (64, 10000.0, (8.0, 1.0, 4.0, 64)), (8, 50.0, (2.0, 0.5, 2.0, 16)), (6, 9.0, None)])
 def test_frequencies_scaled_by_bands_of_the_wavelength(dims, base, sc):
     from infero_b200.parts.rope import RopeNeox
@@ -113,7 +126,7 @@ def test_frequencies_scaled_by_bands_of_the_wavelength(dims, base, sc):
             assert ((ratio > 1.0 / sc[0] + 1e-9) & (ratio < 1.0 - 1e-9)).any()   # and the blend between them
 
 
-@pytest.mark.parametrize("dims,base,sc", [(64, 50000.0, (2.0, 512, 32.0, 1.0)), (64, 5000.0, (4.0, 32, 8.0, 1.0)), (6, 9.0, (3.0, 12, 6.0, 1.0))])
+@pytest.mark.parametrize("dims,base,sc", [(64, 70000.0, (2.5, 256, 32.0, 1.0)), (64, 5000.0, (4.0, 32, 8.0, 1.0)), (6, 9.0, (3.0, 12, 6.0, 1.0))])
 def test_frequencies_scaled_by_a_ramp_over_the_pair_index(dims, base, sc):
     from infero_b200.parts.rope import RopeNeox
     rope = RopeNeox(PositionSpec("rope_neox", base, dims, yarn=sc))
