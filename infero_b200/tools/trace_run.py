@@ -49,7 +49,7 @@ def main(argv=None) -> int:
     n_tok = max(int(args.max_tokens), args.page_size)
     pages = -(-n_tok // args.page_size)
     model, _cfg = load_model(args.model, args.dtype, args.device)
-    ecfg = EngineConfig(dtype=args.dtype, page_size=args.page_size, num_pages=pages, max_seqs=16,
+    ecfg = EngineConfig(dtype=args.dtype, page_size=args.page_size, num_pages=pages, max_seqs=4,
                         ctx=pages * args.page_size, max_batch_tokens=max(pages * args.page_size, 64),
                         max_logit_rows=max(pages * args.page_size, 64), cuda_graphs=False,
                         device=args.device)
