@@ -59,6 +59,40 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, int proj_strid
     if (u16) u16[(size_t)(c / bs) * u16_blk + (size_t)t * bs + (c % bs)] = __float2bfloat16_rn(acc);
 }
 
+// The same for four neighbouring channels a thread (all offsets and C in multiples of four, 16-byte aligned rows).
+__global__ void rglru_conv_vec4_kernel(const float* __restrict__ proj, int proj_stride, int x_off, const float* __restrict__ conv_w,
+                                       const float* __restrict__ conv_b, int taps, const float* __restrict__ state,
+                                       const int* __restrict__ tok_entry, const int* __restrict__ entry_q_start,
+                                       const int* __restrict__ entry_slot, float* __restrict__ u, bf16* __restrict__ u16,
+                                       int bs, long long u16_blk, int n_tokens, int C) {
+    const int C4 = C / 4;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_tokens * C4) return;
+    const int t = (int)(idx / C4), c = (int)(idx % C4) * 4;
+    const int e = tok_entry[t];
+    const int local = t - entry_q_start[e];
+    const float* tail = state + (size_t)entry_slot[e] * taps * C;
+    float4 acc = conv_b ? *reinterpret_cast<const float4*>(conv_b + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        const float* src = back <= local ? proj + (size_t)(t - back) * proj_stride + x_off + c
+                                         : tail + (size_t)(taps - 1 - (back - local)) * C + c;
+        const float4 xv = *reinterpret_cast<const float4*>(src);
+        acc.x = fmaf(conv_w[(size_t)c * taps + j], xv.x, acc.x);
+        acc.y = fmaf(conv_w[(size_t)(c + 1) * taps + j], xv.y, acc.y);
+        acc.z = fmaf(conv_w[(size_t)(c + 2) * taps + j], xv.z, acc.z);
+        acc.w = fmaf(conv_w[(size_t)(c + 3) * taps + j], xv.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(u + (size_t)t * C + c) = acc;
+    if (u16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned*>(&lo);
+        pk.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(u16 + (size_t)(c / bs) * u16_blk + (size_t)t * bs + (c % bs)) = pk;
+    }
+}
+
 constexpr int BM = 64, BN = 64, BK = 16;
 
 // out[t, b * 2 bs + n] = sum_k u[t, b * bs + k] * W[b, n, k],  W [blocks, 2 bs, bs]: the rows of Ra[b], then those of Ri[b]
@@ -110,6 +144,49 @@ rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ wg, float
             const int gn = n0 + tx * 4 + j;
             if (gn < N) out[(size_t)gm * 2 * C + (size_t)b * N + gn] = acc[i][j];
         }
+    }
+}
+
+// Steps of a few tokens with bf16 matrices: a warp per result column, its lanes along the contraction (eight
+// weights a load), the step's tokens in registers; a tree of shuffles adds the lanes up.  Same layout of the results.
+template <int MT>
+__global__ void __launch_bounds__(256)
+rglru_gates_skinny_kernel(const float* __restrict__ u, const bf16* __restrict__ wg, float* __restrict__ out, int M, int C, int bs) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= 2 * C) return;
+    const int N = 2 * bs, b = warp / N, n = warp % N;
+    const bf16* w = wg + ((size_t)b * N + n) * bs;
+    const float* a = u + (size_t)b * bs;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+    for (int k = lane * 8; k < bs; k += 256) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(w + k);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float wv[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p2[i]);
+            wv[2 * i] = f.x, wv[2 * i + 1] = f.y;
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < M) {
+                const float4 a0 = *reinterpret_cast<const float4*>(a + (size_t)m * C + k);
+                const float4 a1 = *reinterpret_cast<const float4*>(a + (size_t)m * C + k + 4);
+                float s = acc[m];
+                s = fmaf(a0.x, wv[0], s), s = fmaf(a0.y, wv[1], s), s = fmaf(a0.z, wv[2], s), s = fmaf(a0.w, wv[3], s);
+                s = fmaf(a1.x, wv[4], s), s = fmaf(a1.y, wv[5], s), s = fmaf(a1.z, wv[6], s), s = fmaf(a1.w, wv[7], s);
+                acc[m] = s;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        float s = acc[m];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0 && m < M) out[(size_t)m * 2 * C + (size_t)b * N + n] = s;
     }
 }
 
@@ -234,9 +311,17 @@ int infero_rglru_conv(const float* proj, int proj_stride, int x_off, const float
     INFERO_REQUIRE(!u_bf16 || (blocks >= 1 && C % blocks == 0 && rows_per_block >= n_tokens), "rglru: bad layout of the bf16 copy");
     const long long total = (long long)n_tokens * C;
     const int bs = u_bf16 ? C / blocks : C;
-    rglru_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(proj, proj_stride, x_off, conv_w, conv_b, taps, state,
-                                                                          tok_entry, entry_q_start, entry_slot, u, (bf16*)u_bf16,
-                                                                          bs, rows_per_block * bs, n_tokens, C);
+    const bool vec4 = C % 4 == 0 && bs % 4 == 0 && proj_stride % 4 == 0 && x_off % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
+                      (uintptr_t)u % 16 == 0 && (uintptr_t)state % 16 == 0 && (!conv_b || (uintptr_t)conv_b % 16 == 0) &&
+                      (!u_bf16 || (uintptr_t)u_bf16 % 8 == 0);
+    if (vec4)
+        rglru_conv_vec4_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(proj, proj_stride, x_off, conv_w, conv_b, taps,
+                                                                                       state, tok_entry, entry_q_start, entry_slot, u,
+                                                                                       (bf16*)u_bf16, bs, rows_per_block * bs, n_tokens, C);
+    else
+        rglru_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(proj, proj_stride, x_off, conv_w, conv_b, taps, state,
+                                                                              tok_entry, entry_q_start, entry_slot, u, (bf16*)u_bf16,
+                                                                              bs, rows_per_block * bs, n_tokens, C);
     return infero_check_launch("rglru_conv");
 }
 
@@ -247,6 +332,13 @@ int infero_rglru_gates(const float* u, const void* wg, int w_dtype, float* out, 
     const int bs = C / blocks, tiles_n = (2 * bs + BN - 1) / BN;
     INFERO_REQUIRE((n_tokens + BM - 1) / BM <= 65535 && blocks <= 65535, "rglru: grid too large");
     dim3 grid(tiles_n, (n_tokens + BM - 1) / BM, blocks);
+    if (w_dtype != INFERO_F32 && n_tokens <= 16 && bs % 8 == 0 && (uintptr_t)wg % 16 == 0 && (uintptr_t)u % 16 == 0) {
+        const unsigned nb = (unsigned)((2ll * C * 32 + 255) / 256);
+        if (n_tokens <= 4) rglru_gates_skinny_kernel<4><<<nb, 256, 0, stream>>>(u, (const bf16*)wg, out, n_tokens, C, bs);
+        else if (n_tokens <= 8) rglru_gates_skinny_kernel<8><<<nb, 256, 0, stream>>>(u, (const bf16*)wg, out, n_tokens, C, bs);
+        else rglru_gates_skinny_kernel<16><<<nb, 256, 0, stream>>>(u, (const bf16*)wg, out, n_tokens, C, bs);
+        return infero_check_launch("rglru_gates_skinny");
+    }
     if (w_dtype == INFERO_F32)
         rglru_gates_kernel<float><<<grid, 256, 0, stream>>>(u, (const float*)wg, out, n_tokens, C, bs);
     else

@@ -149,4 +149,4 @@ class NormedAttention(Mixer):
         proj = self.inp.forward(h, out_dtype=torch.float32)
         act = torch.empty((h.shape[0], self.H * self.V), dtype=h.dtype, device=h.device)
         self.core(ctx, proj, 0, slot, act)
-        return self.out.forward(act, residual=True, out_dtype=torch.float32)
+        return self.out.forward(act, defer=True, residual=True, out_dtype=torch.float32)

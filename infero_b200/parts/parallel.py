@@ -77,4 +77,4 @@ class ParallelMixer(Mixer):
         act = torch.empty((h.shape[0], self.act_width), dtype=h.dtype, device=h.device)
         for b, r, c, s in zip(self.branches, self.row_offsets, self.col_offsets, self.scales):
             b.core(ctx, proj, r, slot, act[:, c:c + b.out_width], s)
-        return self.out.forward(act, residual=True, out_dtype=torch.float32)
+        return self.out.forward(act, defer=True, residual=True, out_dtype=torch.float32)

@@ -92,4 +92,4 @@ class RgLruMixer(Mixer):
         proj = self.inp.forward(h, out_dtype=torch.float32)
         act = torch.empty((h.shape[0], self.C), dtype=h.dtype, device=h.device)
         self.core(ctx, proj, 0, slot, act)
-        return self.out.forward(act, residual=True, out_dtype=torch.float32)
+        return self.out.forward(act, defer=True, residual=True, out_dtype=torch.float32)
