@@ -34,6 +34,34 @@ __device__ __forceinline__ float gelu_tanhf_(float z) {
     return z * __frcp_rn(1.0f + expf(-2.0f * w));
 }
 
+// Where the result is rounded to bf16, the hardware's approximate exponential, reciprocal and root (relative errors of
+// about 1e-6) take the place of the correctly rounded sequences: a third of the scan's instructions.  32-bit results
+// keep the exact forms.
+template <bool FAST> __device__ __forceinline__ float sigmoid_(float z) {
+    if constexpr (FAST) return __fdividef(1.0f, 1.0f + __expf(-z));
+    else return sigmoidf_(z);
+}
+template <bool FAST> __device__ __forceinline__ float gelu_tanh_(float z) {
+    if constexpr (FAST) {
+        const float w = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+        return z * __fdividef(1.0f, 1.0f + __expf(-2.0f * w));
+    } else return gelu_tanhf_(z);
+}
+// exp(x) - 1 for x <= 0: the series where x is small (so that 1 - a^2 keeps its digits), else the exponential
+template <bool FAST> __device__ __forceinline__ float expm1_(float x) {
+    if constexpr (FAST) {
+        const float p = x * (1.0f + x * (0.5f + x * (0.16666667f + x * (0.041666668f + x * 0.0083333338f))));
+        return x > -0.0625f ? p : __expf(x) - 1.0f;
+    } else return expm1f(x);
+}
+template <bool FAST> __device__ __forceinline__ float sqrt_(float x) {
+    if constexpr (FAST) {
+        float r;
+        asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+        return r;
+    } else return sqrtf(x);
+}
+
 constexpr int MAX_TAPS = 16;
 
 __global__ void rglru_conv_kernel(const float* __restrict__ proj, int proj_stride, int x_off, const float* __restrict__ conv_w,
@@ -53,7 +81,7 @@ __global__ void rglru_conv_kernel(const float* __restrict__ proj, int proj_strid
         float xv;
         if (back <= local) xv = proj[(size_t)(t - back) * proj_stride + x_off + c];
         else xv = tail[(size_t)(taps - 1 - (back - local)) * C + c];    // tail row taps-2 is the token just before the portion
-        acc = fmaf(conv_w[(size_t)c * taps + j], xv, acc);
+        acc = fmaf(conv_w[(size_t)j * C + c], xv, acc);
     }
     u[(size_t)t * C + c] = acc;
     if (u16) u16[(size_t)(c / bs) * u16_blk + (size_t)t * bs + (c % bs)] = __float2bfloat16_rn(acc);
@@ -78,10 +106,11 @@ __global__ void rglru_conv_vec4_kernel(const float* __restrict__ proj, int proj_
         const float* src = back <= local ? proj + (size_t)(t - back) * proj_stride + x_off + c
                                          : tail + (size_t)(taps - 1 - (back - local)) * C + c;
         const float4 xv = *reinterpret_cast<const float4*>(src);
-        acc.x = fmaf(conv_w[(size_t)c * taps + j], xv.x, acc.x);
-        acc.y = fmaf(conv_w[(size_t)(c + 1) * taps + j], xv.y, acc.y);
-        acc.z = fmaf(conv_w[(size_t)(c + 2) * taps + j], xv.z, acc.z);
-        acc.w = fmaf(conv_w[(size_t)(c + 3) * taps + j], xv.w, acc.w);
+        const float4 wv = *reinterpret_cast<const float4*>(conv_w + (size_t)j * C + c);
+        acc.x = fmaf(wv.x, xv.x, acc.x);
+        acc.y = fmaf(wv.y, xv.y, acc.y);
+        acc.z = fmaf(wv.z, xv.z, acc.z);
+        acc.w = fmaf(wv.w, xv.w, acc.w);
     }
     *reinterpret_cast<float4*>(u + (size_t)t * C + c) = acc;
     if (u16) {
@@ -202,13 +231,14 @@ constexpr int SEG = 16;              // tokens of a segment
 // neither the width of a block nor what else is in the step changes a bit of the result.
 // gates: the products of token t, block b at gates + t * g_tok + b * g_blk: Ra's bs, then Ri's bs.
 template <typename T, int CH>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(256, 2)
 rglru_scan_kernel(const float* __restrict__ proj, int proj_stride, int y_off, int x_off, const float* __restrict__ u,
                   const float* __restrict__ gates, long long g_tok, long long g_blk, const float* __restrict__ ra_b,
                   const float* __restrict__ ri_b, const float* __restrict__ lam, float slope, int taps,
                   float* __restrict__ state, const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                   const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride, int C, int bs, float scale) {
     constexpr int SUB = 32 / CH;
+    constexpr bool FAST = sizeof(T) == 2;
     extern __shared__ float2 scan_smem[];
     const int threads = blockDim.x, tid = threadIdx.x;
     const int nseg = (threads / 32) * SUB;
@@ -246,12 +276,12 @@ rglru_scan_kernel(const float* __restrict__ proj, int proj_stride, int y_off, in
 #pragma unroll
             for (int j = 0; j < SEG; ++j) {
                 if (k0 + j < k1) {
-                    const float r = sigmoidf_(gr[j] + ba);
-                    const float i = sigmoidf_(gi[j] + bi);
+                    const float r = sigmoid_<FAST>(gr[j] + ba);
+                    const float i = sigmoid_<FAST>(gi[j] + bi);
                     // a = exp(log a) = 1 + e with e = expm1(log a); 1 - a^2 = -e (2 + e) keeps its digits where a is close to 1
-                    const float e = expm1f(-sp * r);
+                    const float e = expm1_<FAST>(-sp * r);
                     const float a = 1.0f + e;
-                    const float b = sqrtf(-e * (2.0f + e)) * (i * uv[j]);
+                    const float b = sqrt_<FAST>(-e * (2.0f + e)) * (i * uv[j]);
                     ab[(size_t)j * threads + tid] = make_float2(a, b);
                     B = fmaf(a, B, b);
                     A *= a;
@@ -276,7 +306,7 @@ rglru_scan_kernel(const float* __restrict__ proj, int proj_stride, int y_off, in
                     if (k0 + j < k1) {
                         const float2 f = ab[(size_t)j * threads + tid];
                         S = fmaf(f.x, S, f.y);
-                        out[(size_t)(t0 + k0 + j) * out_stride + c] = from_f32<T>(S * gelu_tanhf_(yv[j]) * scale);
+                        out[(size_t)(t0 + k0 + j) * out_stride + c] = from_f32<T>(S * gelu_tanh_<FAST>(yv[j]) * scale);
                     }
                 }
             }
@@ -312,7 +342,7 @@ int infero_rglru_conv(const float* proj, int proj_stride, int x_off, const float
     const long long total = (long long)n_tokens * C;
     const int bs = u_bf16 ? C / blocks : C;
     const bool vec4 = C % 4 == 0 && bs % 4 == 0 && proj_stride % 4 == 0 && x_off % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
-                      (uintptr_t)u % 16 == 0 && (uintptr_t)state % 16 == 0 && (!conv_b || (uintptr_t)conv_b % 16 == 0) &&
+                      (uintptr_t)u % 16 == 0 && (uintptr_t)state % 16 == 0 && (uintptr_t)conv_w % 16 == 0 && (!conv_b || (uintptr_t)conv_b % 16 == 0) &&
                       (!u_bf16 || (uintptr_t)u_bf16 % 8 == 0);
     if (vec4)
         rglru_conv_vec4_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(proj, proj_stride, x_off, conv_w, conv_b, taps,
@@ -360,10 +390,11 @@ int infero_rglru_scan(const float* proj, int proj_stride, int y_off, int x_off, 
     INFERO_REQUIRE(blocks >= 1 && C % blocks == 0, "rglru: %d channels in %d blocks", C, blocks);
     const int bs = C / blocks;
     // steps of short portions: a warp of 32 channels per segment, as many warps as the longest portion has segments (two
-    // at most); steps with long portions: 8 channels times 4 segments a warp, 16 warps
+    // at most); steps with long portions: 8 channels times 4 segments a warp, 8 warps, two blocks a multiprocessor, so that
+    // one block's loads overlap the other's arithmetic
     const bool wide = max_q_len > 2 * SEG;
     const int ch = wide ? 8 : 32;
-    const int warps = wide ? 16 : (max_q_len > SEG ? 2 : 1);
+    const int warps = wide ? 8 : (max_q_len > SEG ? 2 : 1);
     const int threads = 32 * warps, nseg = warps * (32 / ch);
     const size_t smem = (size_t)SEG * threads * sizeof(float2) + (size_t)nseg * ch * sizeof(float2) + ch * sizeof(float);
     dim3 grid((C + ch - 1) / ch, n_entries);

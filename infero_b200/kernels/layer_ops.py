@@ -377,14 +377,15 @@ def head_gate(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, 
 def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], w_gates: torch.Tensor,
           ra_b: torch.Tensor, ri_b: torch.Tensor, lam: torch.Tensor, slope: float, state: torch.Tensor, tok_entry,
           entry_q_start, entry_q_len, entry_slot, n_entries: int, out: torch.Tensor, scale: float = 1.0,
-          max_q_len: int = 1, tensor_cores: bool = False) -> None:
+          max_q_len: int = 1, tensor_cores: bool = False, conv_wt: Optional[torch.Tensor] = None) -> None:
     """The gated linear recurrence of every request of the step over its new tokens; see csrc/rglru.cu.  ``proj`` float32
     [T, >= ...] holds the gate branch at ``y_off`` and the recurrent branch at ``x_off`` (C columns each, biases added);
     ``conv_w`` float32 [C, taps]; ``w_gates`` [blocks, 2 C/blocks, C/blocks] (float32 or bf16): per block the rows of Ra,
     then those of Ri; ``state`` float32 [slots, taps, C] (rows 0..taps-2 the convolution's last inputs, row taps-1 the
     recurrent state); ``out`` [T, C] (a column slice allowed) receives S * gelu_tanh(y) * scale.  ``max_q_len``: the
     longest portion of the step.  ``tensor_cores``: the gate products of a long bf16 step run as one grouped
-    tensor-core product over all blocks, from u rounded to bf16 (32-bit sums); otherwise they are 32-bit throughout."""
+    tensor-core product over all blocks, from u rounded to bf16 (32-bit sums); otherwise they are 32-bit throughout.
+    ``conv_wt``: ``conv_w`` laid out tap-major, float32 [taps, C], as the kernels read it (made here when absent)."""
     T = proj.shape[0]
     C, taps = conv_w.shape
     blocks, two_bs, bs = w_gates.shape
@@ -392,6 +393,9 @@ def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps, C)
     assert blocks * bs == C and two_bs == 2 * bs and w_gates.is_contiguous()
     _f32(conv_w, "conv_w"), _f32(conv_b, "conv_b"), _f32(ra_b, "ra_b"), _f32(ri_b, "ri_b"), _f32(lam, "lam")
+    if conv_wt is None:
+        conv_wt = conv_w.t().contiguous()
+    assert conv_wt.dtype == torch.float32 and conv_wt.is_contiguous() and tuple(conv_wt.shape) == (taps, C)
     u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
     L = lib()
     u16 = None
@@ -401,7 +405,7 @@ def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv
         u16 = torch.empty((blocks, rows, bs), dtype=torch.bfloat16, device=proj.device)
         if not LA.grouped_ok(u16, w_gates):
             u16 = None
-    _check(L.infero_rglru_conv(_ptr(proj), c_int(proj.stride(0)), c_int(x_off), _ptr(conv_w), _ptr(conv_b), c_int(taps),
+    _check(L.infero_rglru_conv(_ptr(proj), c_int(proj.stride(0)), c_int(x_off), _ptr(conv_wt), _ptr(conv_b), c_int(taps),
                                _ptr(state), _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(entry_q_start, "entry_q_start")),
                                _ptr(_i32(entry_slot, "entry_slot")), _ptr(u), _ptr(u16), c_int(blocks), c_longlong(rows), c_int(T),
                                c_int(C), _stream()))

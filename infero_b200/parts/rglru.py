@@ -61,6 +61,7 @@ class RgLruMixer(Mixer):
         self._bias = torch.cat([f32("y_bias"), f32("x_bias")]).contiguous()
         self.inp = Linear(self._rows, self._bias, f"{self.prefix}.yx")
         self.conv_w, self.conv_b = f32("conv"), f32("conv_bias")
+        self.conv_wt = self.conv_w.t().contiguous()          # tap-major, as the convolution kernel reads it
         ra, ri = tensors[self._n("ra", False)], tensors[self._n("ri", False)]
         if ra.dtype != ri.dtype:
             ra, ri = ra.float(), ri.float()
@@ -86,7 +87,7 @@ class RgLruMixer(Mixer):
         L.rglru(proj, off, off + self.C, self.conv_w, self.conv_b, self.w_gates, self.ra_b, self.ri_b, self.lam,
                 float(self.spec.rec_slope), ctx.state(slot.cache), ctx.tok_entry, ctx.entry_q_start, ctx.entry_q_len,
                 ctx.entry_slot, ctx.n_entries, out, scale, max_q_len=longest,
-                tensor_cores=ctx.act_dtype == torch.bfloat16)
+                tensor_cores=ctx.act_dtype == torch.bfloat16, conv_wt=self.conv_wt)
 
     def forward(self, ctx, h, slot):
         proj = self.inp.forward(h, out_dtype=torch.float32)

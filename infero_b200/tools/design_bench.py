@@ -554,12 +554,13 @@ def time_banelix_kernels(z, T, context, batch, timer, peaks):
         bs = C // nb
         yx = rnd(n, 2 * C, dtype=torch.float32)
         cw, cb = rnd(C, taps, dtype=torch.float32, k=0.3), rnd(C, dtype=torch.float32, k=0.1)
+        cwt = cw.t().contiguous()
         wg = rnd(nb, 2 * bs, bs, k=bs ** -0.5)
         rb, ib, lam = rnd(C, dtype=torch.float32, k=0.1), rnd(C, dtype=torch.float32, k=0.1), rnd(C, dtype=torch.float32)
         state = torch.zeros(len(q_lens), taps, C, device=dev)
         ro = torch.empty(n, C, dtype=bf, device=dev)
         ms = timer(lambda: L.rglru(yx, 0, C, cw, cb, wg, rb, ib, lam, 8.0, state, rctx.tok_entry, rctx.entry_q_start, rctx.entry_q_len,
-                                   rctx.entry_slot, len(q_lens), ro, 0.7, max_q_len=max(q_lens), tensor_cores=True))
+                                   rctx.entry_slot, len(q_lens), ro, 0.7, max_q_len=max(q_lens), tensor_cores=True, conv_wt=cwt))
         least = n * C * (8.0 + 2.0) + 2.0 * wg.numel() + 8.0 * len(q_lens) * taps * C
         moved = least + n * C * (4.0 + 2.0 + 4.0 + 8.0 + 8.0 + 4.0)           # u written and read twice (+ bf16), gates written and read
         note(f"rglru_{label}", ms, least, 2.0 * n * 2 * C * bs, gb_s_with_intermediates=round(moved / ms / 1e6, 1),
