@@ -327,6 +327,67 @@ rglru_scan_kernel(const float* __restrict__ proj, int proj_stride, int y_off, in
     }
 }
 
+// Steps in which every request brings one token, bf16 matrices, blocks of up to 256 channels: convolution, gate
+// products and the state's update in one launch.  A thread block owns one block of channels of one request (so nothing
+// it reads of the state is written by another): u of the block's channels into shared memory, a warp per gate row
+// (eight weights a load, lanes along the contraction), then a thread per channel updates S, writes the result and
+// shifts the convolution's tail.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rglru_step_kernel(const float* __restrict__ proj, int proj_stride, int y_off, int x_off, const float* __restrict__ conv_wt,
+                  const float* __restrict__ conv_b, int taps, const bf16* __restrict__ wg, const float* __restrict__ ra_b,
+                  const float* __restrict__ ri_b, const float* __restrict__ lam, float slope, float* __restrict__ state,
+                  const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
+                  const int* __restrict__ entry_slot, T* __restrict__ out, int out_stride, int C, int bs, float scale) {
+    constexpr bool FAST = sizeof(T) == 2;
+    __shared__ __align__(16) float us[256];
+    __shared__ float xs[256], gs[512];
+    const int b = blockIdx.x, e = blockIdx.y, tid = threadIdx.x;
+    if (entry_q_len[e] <= 0) return;
+    const size_t t = (size_t)entry_q_start[e];
+    float* st = state + (size_t)entry_slot[e] * taps * C;
+    const int c = b * bs + tid;
+    if (tid < bs) {
+        // tail row j holds the input taps-1-j tokens back, which tap j multiplies; the last tap takes this token's
+        const float x = proj[t * proj_stride + x_off + c];
+        float acc = conv_b ? conv_b[c] : 0.f;
+        for (int j = 0; j < taps - 1; ++j) acc = fmaf(conv_wt[(size_t)j * C + c], st[(size_t)j * C + c], acc);
+        acc = fmaf(conv_wt[(size_t)(taps - 1) * C + c], x, acc);
+        us[tid] = acc, xs[tid] = x;
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    const bf16* W = wg + (size_t)b * 2 * bs * bs;
+    for (int n = warp; n < 2 * bs; n += 8) {
+        float s = 0.f;
+        const int k = lane * 8;
+        if (k < bs) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(W + (size_t)n * bs + k);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float4 a0 = *reinterpret_cast<const float4*>(us + k), a1 = *reinterpret_cast<const float4*>(us + k + 4);
+            const float2 w0 = __bfloat1622float2(p2[0]), w1 = __bfloat1622float2(p2[1]);
+            const float2 w2 = __bfloat1622float2(p2[2]), w3 = __bfloat1622float2(p2[3]);
+            s = fmaf(a0.x, w0.x, s), s = fmaf(a0.y, w0.y, s), s = fmaf(a0.z, w1.x, s), s = fmaf(a0.w, w1.y, s);
+            s = fmaf(a1.x, w2.x, s), s = fmaf(a1.y, w2.y, s), s = fmaf(a1.z, w3.x, s), s = fmaf(a1.w, w3.y, s);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) gs[n] = s;
+    }
+    __syncthreads();
+    if (tid < bs) {
+        const float r = sigmoid_<FAST>(gs[tid] + ra_b[c]);
+        const float i = sigmoid_<FAST>(gs[bs + tid] + ri_b[c]);
+        const float e1 = expm1_<FAST>(-slope * softplusf_(lam[c]) * r);
+        const float a = 1.0f + e1;
+        const float S = fmaf(a, st[(size_t)(taps - 1) * C + c], sqrt_<FAST>(-e1 * (2.0f + e1)) * (i * us[tid]));
+        st[(size_t)(taps - 1) * C + c] = S;
+        out[t * out_stride + c] = from_f32<T>(S * gelu_tanh_<FAST>(proj[t * proj_stride + y_off + c]) * scale);
+        for (int j = 0; j + 2 < taps; ++j) st[(size_t)j * C + c] = st[(size_t)(j + 1) * C + c];
+        if (taps >= 2) st[(size_t)(taps - 2) * C + c] = xs[tid];
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -415,6 +476,29 @@ int infero_rglru_scan(const float* proj, int proj_stride, int y_off, int x_off, 
     }
 #undef LAUNCH
     return infero_check_launch("rglru_scan");
+}
+
+// The whole recurrence of a step of single tokens in one launch (bf16 gate matrices, blocks of 8 .. 256 channels in
+// multiples of 8); conv_wt tap-major [taps, C].  Returns 2 without launching where the sizes do not fit.
+int infero_rglru_step(const float* proj, int proj_stride, int y_off, int x_off, const float* conv_wt, const float* conv_b,
+                      int taps, const void* wg, const float* ra_b, const float* ri_b, const float* lam, float slope,
+                      float* state, const int* entry_q_start, const int* entry_q_len, const int* entry_slot, void* out,
+                      int out_stride, int out_dtype, int n_entries, int C, int blocks, float scale, cudaStream_t stream) {
+    if (n_entries == 0) return 0;
+    INFERO_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "rglru: %d taps outside 1..%d", taps, MAX_TAPS);
+    INFERO_REQUIRE(blocks >= 1 && C % blocks == 0, "rglru: %d channels in %d blocks", C, blocks);
+    const int bs = C / blocks;
+    if (bs > 256 || bs % 8 || (uintptr_t)wg % 16 || n_entries > 65535) return 2;
+    dim3 grid(blocks, n_entries);
+    if (out_dtype == INFERO_F32)
+        rglru_step_kernel<float><<<grid, 256, 0, stream>>>(proj, proj_stride, y_off, x_off, conv_wt, conv_b, taps, (const bf16*)wg, ra_b,
+                                                           ri_b, lam, slope, state, entry_q_start, entry_q_len, entry_slot,
+                                                           (float*)out, out_stride, C, bs, scale);
+    else
+        rglru_step_kernel<bf16><<<grid, 256, 0, stream>>>(proj, proj_stride, y_off, x_off, conv_wt, conv_b, taps, (const bf16*)wg, ra_b,
+                                                          ri_b, lam, slope, state, entry_q_start, entry_q_len, entry_slot,
+                                                          (bf16*)out, out_stride, C, bs, scale);
+    return infero_check_launch("rglru_step");
 }
 
 }  // extern "C"

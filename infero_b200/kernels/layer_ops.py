@@ -396,8 +396,18 @@ def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv
     if conv_wt is None:
         conv_wt = conv_w.t().contiguous()
     assert conv_wt.dtype == torch.float32 and conv_wt.is_contiguous() and tuple(conv_wt.shape) == (taps, C)
-    u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
     L = lib()
+    if int(max_q_len) == 1 and w_gates.dtype == torch.bfloat16 and bs % 8 == 0 and bs <= 256:
+        # a step of single tokens: one launch for convolution, gate products and the state's update
+        rc = L.infero_rglru_step(_ptr(proj), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(conv_wt), _ptr(conv_b),
+                                 c_int(taps), _ptr(w_gates), _ptr(ra_b), _ptr(ri_b), _ptr(lam), c_float(slope), _ptr(state),
+                                 _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
+                                 _ptr(_i32(entry_slot, "entry_slot")), _ptr(out), c_int(out.stride(0)), c_int(_dt(out)),
+                                 c_int(n_entries), c_int(C), c_int(blocks), c_float(scale), _stream())
+        if rc != 2:
+            _check(rc)
+            return
+    u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
     u16 = None
     rows = -(-T // 128) * 128
     if tensor_cores and T > 256 and w_gates.dtype == torch.bfloat16:

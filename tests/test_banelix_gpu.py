@@ -405,6 +405,57 @@ def test_a_state_lasts_for_hundreds_of_tokens():
     assert _rel(torch.cat(outs)[:, H * D:H * D + C], want) < 3e-5
 
 
+@pytest.mark.parametrize("C,blocks,taps,out_dtype", [(64, 2, 4, torch.float32), (256, 1, 1, torch.float32), (48, 6, 2, torch.float32),
+                                                     (512, 2, 3, torch.bfloat16)])
+def test_single_token_steps_in_one_launch_with_bf16_gate_matrices(C, blocks, taps, out_dtype):
+    """Steps of single tokens with bf16 gate matrices take one kernel for convolution, gates and state.  Three requests
+    in shuffled slots decode twelve tokens each after a two-token portion (which takes the three-kernel path); every
+    result is held to a 64-bit recurrence written out here."""
+    from infero_b200.kernels import layer_ops as L
+    g = torch.Generator().manual_seed(C + taps)
+    bs, E, n = C // blocks, 3, 14
+    rnd = lambda *sh, k=1.0: torch.randn(*sh, generator=g) * k                                  # noqa: E731
+    yx = rnd(E, n, 2 * C)
+    cw, cb = rnd(C, taps, k=0.5), rnd(C, k=0.1)
+    wg = (rnd(blocks, 2 * bs, bs, k=2.0 * bs ** -0.5)).bfloat16()
+    rb, ib, lam = rnd(C, k=0.3), rnd(C, k=0.3), rnd(C) - 2.0
+    # plain, in 64-bit
+    want = torch.zeros(E, n, C, dtype=torch.float64)
+    W = wg.double()
+    for e in range(E):
+        x = torch.cat([torch.zeros(taps - 1, C, dtype=torch.float64), yx[e, :, C:].double()])
+        S = torch.zeros(C, dtype=torch.float64)
+        for t in range(n):
+            u = cb.double() + sum(cw[:, j].double() * x[t + j] for j in range(taps))
+            ub = u.view(blocks, bs)
+            pre = torch.einsum("bnk,bk->bn", W, ub)
+            r = torch.sigmoid(pre[:, :bs].reshape(C) + rb.double())
+            i = torch.sigmoid(pre[:, bs:].reshape(C) + ib.double())
+            a = torch.exp(-8.0 * r * torch.nn.functional.softplus(lam.double()))
+            S = a * S + torch.sqrt(1.0 - a * a) * i * u
+            y = yx[e, t, :C].double()
+            want[e, t] = 0.9 * S * 0.5 * y * (1.0 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+    dev = lambda t: t.to(DEV)                                                                  # noqa: E731
+    state = torch.full((5, taps, C), 7.0, device=DEV)
+    slots = [4, 1, 2]
+    for sl in slots:
+        state[sl].zero_()
+    cwd, cbd, wgd, rbd, ibd, lamd = dev(cw), dev(cb), dev(wg), dev(rb), dev(ib), dev(lam)
+    got = torch.zeros(E, n, C, dtype=torch.float64)
+
+    def step(at, size):
+        rows = dev(torch.cat([yx[e, at:at + size] for e in range(E)]).contiguous())
+        out = torch.empty(E * size, C, dtype=out_dtype, device=DEV)
+        L.rglru(rows, 0, C, cwd, cbd, wgd, rbd, ibd, lamd, 8.0, state, _i32(np.repeat(np.arange(E), size)),
+                _i32(np.arange(E) * size), _i32([size] * E), _i32(slots), E, out, 0.9, max_q_len=size)
+        got[:, at:at + size] = out.double().cpu().view(E, size, C)
+    step(0, 2)
+    for t in range(2, n):
+        step(t, 1)
+    assert _rel(got, want) < (2e-5 if out_dtype == torch.float32 else 1e-2)
+    assert float(state[0].min()) == 7.0 and float(state[3].max()) == 7.0            # other requests' slots untouched
+
+
 def test_a_far_key_is_found_by_the_left_mixer():
     """Causal attention over all keys: the key that carries the weight is hundreds of tokens back, at page borders."""
     H, G, D, C, d = 2, 1, 64, 64, 192
