@@ -356,23 +356,35 @@ rglru_step_kernel(const float* __restrict__ proj, int proj_stride, int y_off, in
         us[tid] = acc, xs[tid] = x;
     }
     __syncthreads();
+    // a row of the gate matrices takes bs / 8 lanes (a power of two of them): a warp works on 32 / lanes rows at a time,
+    // four such groups per turn with their loads issued together
     const int warp = tid >> 5, lane = tid & 31;
+    int lanes = 1;
+    while (lanes * 8 < bs) lanes <<= 1;
+    const int per = 32 / lanes, sub = lane / lanes, k = (lane % lanes) * 8;
+    const bool in = k < bs;
     const bf16* W = wg + (size_t)b * 2 * bs * bs;
-    for (int n = warp; n < 2 * bs; n += 8) {
-        float s = 0.f;
-        const int k = lane * 8;
-        if (k < bs) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(W + (size_t)n * bs + k);
-            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            const float4 a0 = *reinterpret_cast<const float4*>(us + k), a1 = *reinterpret_cast<const float4*>(us + k + 4);
-            const float2 w0 = __bfloat1622float2(p2[0]), w1 = __bfloat1622float2(p2[1]);
-            const float2 w2 = __bfloat1622float2(p2[2]), w3 = __bfloat1622float2(p2[3]);
-            s = fmaf(a0.x, w0.x, s), s = fmaf(a0.y, w0.y, s), s = fmaf(a0.z, w1.x, s), s = fmaf(a0.w, w1.y, s);
-            s = fmaf(a1.x, w2.x, s), s = fmaf(a1.y, w2.y, s), s = fmaf(a1.z, w3.x, s), s = fmaf(a1.w, w3.y, s);
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    if (in) a0 = *reinterpret_cast<const float4*>(us + k), a1 = *reinterpret_cast<const float4*>(us + k + 4);
+    for (int n0 = warp * per * 4; n0 < 2 * bs; n0 += 8 * per * 4) {
+        uint4 raw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int n = n0 + q * per + sub;
+            raw[q] = (in && n < 2 * bs) ? *reinterpret_cast<const uint4*>(W + (size_t)n * bs + k) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) gs[n] = s;
+        for (int q = 0; q < 4; ++q) {
+            const int n = n0 + q * per + sub;
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[q]);
+            const float2 w0 = __bfloat1622float2(p2[0]), w1 = __bfloat1622float2(p2[1]);
+            const float2 w2 = __bfloat1622float2(p2[2]), w3 = __bfloat1622float2(p2[3]);
+            float s = 0.f;
+            s = fmaf(a0.x, w0.x, s), s = fmaf(a0.y, w0.y, s), s = fmaf(a0.z, w1.x, s), s = fmaf(a0.w, w1.y, s);
+            s = fmaf(a1.x, w2.x, s), s = fmaf(a1.y, w2.y, s), s = fmaf(a1.z, w3.x, s), s = fmaf(a1.w, w3.y, s);
+            for (int o = lanes >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane % lanes == 0 && n < 2 * bs) gs[n] = s;
+        }
     }
     __syncthreads();
     if (tid < bs) {
