@@ -68,7 +68,7 @@ C = {"architecture": "Banelix", "vocab": 61, "width": 40, "norm": {"eps": 1e-5},
 # D: heads of 128 and a long window for the bf16 kernels; four taps; borrowed keys with the same window
 D = {"architecture": "Banelix", "vocab": 301, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
      "residual_mult": 0.4, "layers": [
-         _layer("parallel", _par(_left(4, 2, 128, 0.09, dims=64, bands=(8.0, 1.0, 4.0, 64)), 256, 4, 4, ls=0.6, rs=0.9), 256),
+         _layer("parallel", _par(_left(4, 2, 128, 0.09, dims=64, bands=(8.0, 1.0, 4.0, 64)), 256, 4, 4, ls=0.8, rs=1.2), 256),
          _layer("attention", _att(4, 1, 128, 128, 0.09, 100, ramp=(2.0, 64, 16.0, 1.0)), 256),
          _layer("attention", _att(4, 1, 128, 128, 0.09, 100, ramp=(2.0, 64, 16.0, 1.0), kv_from=1), 256)]}
 CONFIGS = {"A": A, "B": B, "C": C, "D": D}
