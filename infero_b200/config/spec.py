@@ -44,7 +44,8 @@ HGRN2_NAMES = (("q", "mix.q"), ("f", "mix.f"), ("f_bias", "mix.f.b"), ("lower", 
 MOE_NAMES = (("expert", "mlp.e{}"), ("gate", "gate"), ("up", "up"), ("down", "down"), ("router", "mlp.router"),
              ("shared", "mlp.shared"), ("shared_gate", "mlp.shared.sg"))
 LATENT_ATTENTION_NAMES = (("q", "mix.q"), ("down", "mix.dkv"), ("latent_norm", "mix.dkv.norm"), ("up_k", "mix.uk"),
-                          ("up_v", "mix.uv"), ("gate", "mix.g"), ("o", "mix.o"))
+                          ("up_v", "mix.uv"), ("gate", "mix.g"), ("o", "mix.o"),
+                          ("q_down", "mix.dq"), ("q_norm", "mix.dq.norm"), ("q_up", "mix.uq"))
 RELU2_NAMES = (("up", "mlp.up"), ("down", "mlp.down"))
 MOE_GROUPED_NAMES = (("expert", "mlp.e{}"), ("gate", "gate"), ("up", "up"), ("down", "down"), ("router", "mlp.router"),
                      ("correction", "mlp.correction"), ("shared", "mlp.shared"))
@@ -54,9 +55,13 @@ NORMED_ATTENTION_NAMES = (("q", "mix.q"), ("k", "mix.k"), ("v", "mix.v"), ("o", 
 RGLRU_NAMES = (("y", "mix.y"), ("y_bias", "mix.y.b"), ("x", "mix.x"), ("x_bias", "mix.x.b"), ("conv", "mix.conv"),
                ("conv_bias", "mix.conv.b"), ("ra", "mix.ra"), ("ra_bias", "mix.ra.b"), ("ri", "mix.ri"),
                ("ri_bias", "mix.ri.b"), ("lam", "mix.lam"), ("o", "mix.o"))
+SSD_NAMES = (("in", "mix.in"), ("conv", "mix.conv"), ("conv_bias", "mix.conv.b"), ("dt_bias", "mix.dt_bias"),
+             ("a_log", "mix.A_log"), ("skip", "mix.D"), ("out_norm", "mix.norm"), ("o", "mix.o"))
+MOE_SCORED_NAMES = (("expert", "mlp.e{}"), ("up", "up"), ("down", "down"), ("router", "mlp.router"), ("shared", "mlp.shared"))
 MIXER_NAMES = {"diff_attention": DIFF_ATTENTION_NAMES, "hgrn2": HGRN2_NAMES, "latent_attention": LATENT_ATTENTION_NAMES,
-               "normed_attention": NORMED_ATTENTION_NAMES, "rglru": RGLRU_NAMES, "parallel": ()}
-FEED_FORWARD_NAMES = {"moe_swiglu": MOE_NAMES, "relu2": RELU2_NAMES, "moe_grouped": MOE_GROUPED_NAMES}
+               "normed_attention": NORMED_ATTENTION_NAMES, "rglru": RGLRU_NAMES, "parallel": (), "ssd": SSD_NAMES}
+FEED_FORWARD_NAMES = {"moe_swiglu": MOE_NAMES, "relu2": RELU2_NAMES, "moe_grouped": MOE_GROUPED_NAMES,
+                      "moe_scored": MOE_SCORED_NAMES}
 
 
 @dataclass(frozen=True)
@@ -117,13 +122,16 @@ class MixerSpec:
     product gives ``latent_dim`` numbers (RMS-normed with a weight: the latent c) and ``rot_dim`` more (a rotated key
     part shared by all heads); head n's key is [Wuk_n c | that part] (``head_dim`` + ``rot_dim`` wide, like its
     query), its value Wuv_n c (``value_dim`` wide).  ``position`` turns the ``rot_dim`` parts of queries and keys
-    (its ``rotary_dim`` <= ``rot_dim``).  ``out_gate``: head n's result is multiplied by sigmoid of the n-th row of
-    one more product of the mixer's input.  Causal softmax over all keys, ``scale`` as given.
+    (its ``rotary_dim`` <= ``rot_dim``; ``rot_dim`` 0: no rotated part at all).  ``out_gate``: head n's result is
+    multiplied by sigmoid of the n-th row of one more product of the mixer's input.  Causal softmax over all keys,
+    ``scale`` as given.  ``q_latent_dim`` > 0: the queries go through a latent of their own, q = Wuq rms(Wdq h) w.
 
     kind "normed_attention": grouped-query attention whose queries and keys are normed.  ``qk_norm_kind``
     "projection": an RMS norm with a weight over the whole query projection (all heads at once) and over the whole key
     projection, before the rotation; "head_unit": every head of q and k divided by its root mean square (no weight)
-    after the rotation; "": none.  ``value_from_key``: there is no value projection, a key's value is the key as it
+    after the rotation; "head": an RMS norm over every head of q and of k with a weight of ``head_dim`` numbers shared by
+    the heads (one for q, one for k), before the rotation; "": none.  ``distance_slope_exp`` = b > 0: head h's score
+    loses s_h (i - j) for a key j seen from position i, with s_h = 2^(-b (h + 1) / H).  ``value_from_key``: there is no value projection, a key's value is the key as it
     was projected (before norm and rotation).  ``sink``: the softmax's denominator has one more term exp(0) without a
     value.  ``out_gate`` as above.  ``borrows_cache``: the layer has no key or value tensors at all and reads the cache
     another schedule entry writes (its ``ScheduleEntry.write_cache`` is False).  ``keep_window``: how many keys the
@@ -134,6 +142,13 @@ class MixerSpec:
     recurrent branch u = conv(Wx h + b) (a causal convolution of ``conv_taps`` taps per channel, with a bias); per
     block of rec_width / ``rec_blocks`` channels r = sigmoid(Ra u + b), i = sigmoid(Ri u + b);
     a = exp(-``rec_slope`` r softplus(lam)); S <- a S + sqrt(1 - a^2) i u; result Wo (S * y).
+
+    kind "ssd": a selective state-space recurrence with a scalar decay per head (the state-space-duality form).  One
+    input product gives [z | x | B | C | dt] with x and z ``num_heads`` * ``value_dim`` wide, B and C ``rec_groups`` *
+    ``state_dim`` wide and one dt per head; x, B and C pass a causal convolution of ``conv_taps`` taps per channel (with a
+    bias) and silu; dt = softplus(dt + dt_bias); per head S <- exp(-exp(A_log) dt) S + dt B x^T (S ``state_dim`` x
+    ``value_dim``), y = S^T C + D x; y silu(z) is RMS-normed in ``norm_groups`` equal parts, times a weight, and goes
+    through the output product.
 
     kind "parallel": the mixers of ``branches`` read the same input side by side; the result is the sum of their
     results times ``branch_scales``.  Branch b's tensors carry the leaf names of its own spec.
@@ -161,6 +176,11 @@ class MixerSpec:
     sink: bool = False
     borrows_cache: bool = False
     keep_window: Optional[int] = None
+    distance_slope_exp: float = 0.0   # > 0: a distance bias with slopes 2^(-this (h + 1) / H) is taken off the scores
+    q_latent_dim: int = 0             # latent attention: width of the queries' own latent; 0: a direct query product
+    state_dim: int = 0                # ssd: rows of a head's state
+    rec_groups: int = 1               # ssd: groups of heads that share B and C
+    norm_groups: int = 1              # ssd: equal parts the gated result is normed in
     rec_width: int = 0
     rec_blocks: int = 1
     rec_slope: float = 8.0
@@ -202,7 +222,13 @@ class FeedForwardSpec:
     s = softmax of the router's logits over all experts; experts are picked by s + a stored per-expert correction
     (``route_correction``), among the ``route_keep`` best of ``route_groups`` groups of neighbouring experts (a
     group's score: its largest pick score); weights are s of the ``top`` picked over their sum.  With
-    ``shared_intermediate`` > 0 an expert of that width (limit ``shared_limit``) runs for every token and is added."""
+    ``shared_intermediate`` > 0 an expert of that width (limit ``shared_limit``) runs for every token and is added.
+
+    kind "moe_scored": experts of the ungated form down(act(up(x))) with ``activation`` "relu2".  Every expert's score is
+    ``route_score`` of its router logit ("sigmoid"); the ``top`` largest are chosen (the lowest index wins a tie); the
+    weights are the chosen scores, divided by their sum only where ``route_renorm`` says so; with ``weight_input`` the
+    weight multiplies what the expert reads (the result is sum_c expert_c(w_c x)), else what it returns.  With
+    ``shared_intermediate`` > 0 an expert of the same form and that width runs for every token and is added."""
     kind: str
     hidden: int
     intermediate: int
@@ -216,6 +242,9 @@ class FeedForwardSpec:
     route_groups: int = 1
     route_keep: int = 1
     route_correction: bool = False
+    route_score: str = "softmax"
+    route_renorm: bool = True
+    weight_input: bool = False
     extra: Tuple[Tuple[str, object], ...] = ()
     names: Tuple[Tuple[str, str], ...] = ()          # role -> leaf name (see SWIGLU_NAMES)
     weight_suffix: str = ".weight"

@@ -1,7 +1,8 @@
 // Attention over the paged cache for any batch of tokens: one warp per (token, query head).
 //
 // For token t of request entry e at position p, head h (kv head h / group):
-//   s_j = (q . K[j]) * scale   for lo <= j <= p,  lo = window ? max(0, p - window + 1) : 0
+//   s_j = (q . K[j]) * scale - slope_h * (p - j)   for lo <= j <= p,  lo = window ? max(0, p - window + 1) : 0
+//   (slope_h: a per-head distance bias, zero where the caller gives no slopes)
 //   out = sum_j softmax(s)_j V[j]
 // (crates/kernels/src/cu/ops.cu:709-811 is the reference's three-kernel statement; its
 // fused decode kernel is ops.cu:1773-2075.  Contiguous head groups: kv head = h / group.)
@@ -26,7 +27,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tok_entry, const int* __restrict__ positions,
                          int n_tokens, int n_heads, int n_kv, int head_dim, int value_dim, int page_size,
-                         int window, float scale, int sink) {
+                         int window, float scale, int sink, const float* __restrict__ slopes) {
     __shared__ float q_s[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -37,6 +38,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int pos = positions[t];
     const int* table = block_table + (size_t)tok_entry[t] * max_blocks;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const float slope = slopes ? slopes[h] : 0.f;
 
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * head_dim;
     for (int i = lane; i < head_dim; i += 32) q_s[warp][i] = to_f32(qrow[i]);
@@ -61,7 +63,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 const T* kr = k_cache + row * head_dim;
                 float d = 0.f;
                 for (int i = 0; i < head_dim; ++i) d = fmaf(q_s[warp][i], to_f32(kr[i]), d);
-                s = d * scale;
+                s = d * scale - slope * (float)(pos - j);
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -98,12 +100,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 extern "C" {
 
 // Keys of width head_dim, values of width value_dim (the cache's two arrays have their own row widths); ``sink``:
-// the softmax's denominator has one more term exp(0), which carries no value.
-int infero_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                                const void* v_cache, int dtype, const int* block_table, int max_blocks,
-                                const int* tok_entry, const int* positions, int n_tokens, int n_heads,
-                                int n_kv, int head_dim, int value_dim, int page_size, int window, float scale,
-                                int sink, cudaStream_t stream) {
+// the softmax's denominator has one more term exp(0), which carries no value; ``slopes``: float32 [n_heads] or null,
+// head h's score loses slopes[h] times the distance between the query and the key.
+int infero_attention_generic_bias(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                  const void* v_cache, int dtype, const int* block_table, int max_blocks,
+                                  const int* tok_entry, const int* positions, int n_tokens, int n_heads,
+                                  int n_kv, int head_dim, int value_dim, int page_size, int window, float scale,
+                                  int sink, const float* slopes, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(head_dim >= 1 && head_dim <= MAX_D, "attention: head_dim %d outside 1..%d", head_dim, MAX_D);
     INFERO_REQUIRE(value_dim >= 1 && value_dim <= MAX_D, "attention: value width %d outside 1..%d", value_dim, MAX_D);
@@ -113,12 +116,22 @@ int infero_attention_generic_ex(const void* q, int q_stride, void* out, int out_
     if (dtype == INFERO_F32)
         attention_generic_kernel<float><<<blocks, WARPS * 32, 0, stream>>>((const float*)q, q_stride, (float*)out,
             out_stride, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks, tok_entry,
-            positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size, window, scale, sink);
+            positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size, window, scale, sink, slopes);
     else
         attention_generic_kernel<bf16><<<blocks, WARPS * 32, 0, stream>>>((const bf16*)q, q_stride, (bf16*)out,
             out_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, tok_entry,
-            positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size, window, scale, sink);
+            positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size, window, scale, sink, slopes);
     return infero_check_launch("attention_generic");
+}
+
+int infero_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                const void* v_cache, int dtype, const int* block_table, int max_blocks,
+                                const int* tok_entry, const int* positions, int n_tokens, int n_heads,
+                                int n_kv, int head_dim, int value_dim, int page_size, int window, float scale,
+                                int sink, cudaStream_t stream) {
+    return infero_attention_generic_bias(q, q_stride, out, out_stride, k_cache, v_cache, dtype, block_table, max_blocks,
+                                         tok_entry, positions, n_tokens, n_heads, n_kv, head_dim, value_dim, page_size,
+                                         window, scale, sink, nullptr, stream);
 }
 
 int infero_attention_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,

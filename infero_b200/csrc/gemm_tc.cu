@@ -1406,8 +1406,8 @@ int infero_gemm_tc_act(const void* x, const void* w, void* out, int M, int N, in
 }
 
 // A grouped product on the persistent kernel: x [M, K] in tiles of 128 rows, w n_groups stacked [N, K] matrices,
-// tile m of x multiplies matrix tile_group[m] (device int32 [ceil(M / 128)]).  swiglu: w's rows alternate gate and
-// up and out is bf16 [M, N / 2]; else out is float32 [M, N].
+// tile m of x multiplies matrix tile_group[m] (device int32 [ceil(M / 128)]).  swiglu 1: w's rows alternate gate and
+// up and out is bf16 [M, N / 2]; 2: out is bf16 [M, N], the squared relu of the product; 0: out is float32 [M, N].
 // With a gated activation the pair (gate, up) goes through glu_act(act_kind, act_limit, act_alpha) of common.cuh.
 int infero_gemm_tc_grouped(const void* x, const void* w, void* out, int swiglu, int M, int N, int K, int ldx, int ldc,
                            const int* tile_group, int n_groups, int sm_count, int act_kind, float act_limit,
@@ -1417,6 +1417,11 @@ int infero_gemm_tc_grouped(const void* x, const void* w, void* out, int swiglu, 
     INFERO_REQUIRE(tile_group && n_groups >= 1 && (long long)N * n_groups < (1ll << 31), "gemm_tc_grouped: bad groups");
     int* err;
     if (err_flag_ptr(&err)) return 1;
+    if (swiglu == 2) {
+        INFERO_REQUIRE(ldc >= N, "gemm_tc_grouped: ldc=%d below N=%d", ldc, N);
+        return launch_persistent<EPI_ROW, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream, tile_group,
+                                                n_groups, ACT_RELU2);
+    }
     if (swiglu) {
         INFERO_REQUIRE(N % 2 == 0 && ldc >= N / 2, "gemm_tc_grouped: N=%d must be even and ldc=%d at least N/2", N, ldc);
         return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream,

@@ -52,7 +52,8 @@ __device__ __forceinline__ float rotated(const float* __restrict__ part, int i, 
 
 template <typename T>
 __global__ void __launch_bounds__(PREP_THREADS)
-latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off, int kv_off,
+latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ q_src, int q_stride,
+                      int q_off, int kv_off,
                       const float* __restrict__ norm_w, float eps, const double* __restrict__ freq, int rot, int pairing,
                       float amp, const int* __restrict__ positions, const int* __restrict__ tok_entry,
                       const int* __restrict__ block_table, int max_blocks, int page_size, T* __restrict__ cache,
@@ -78,7 +79,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off
     }
     // the queries of heads [n0, n1)
     const int n0 = (blockIdx.y - 1) * heads_per_block, n1 = min(H, n0 + heads_per_block);
-    const float* q = row + q_off;
+    const float* q = q_src + (size_t)t * q_stride + q_off;
     for (int i = n0 * D + threadIdx.x; i < n1 * D; i += blockDim.x) {
         const int n = i / D, c = i % D;
         q_plain[((size_t)n * head_rows + t) * D + c] = from_f32<T>(q[(size_t)n * (D + R) + c]);
@@ -175,9 +176,12 @@ __global__ void latent_finish_kernel(const float* __restrict__ val, long long he
 
 extern "C" {
 
-// proj float32 [T, proj_stride]: the query's H * (D + R) columns from q_off, the C + R columns of the latent row from
-// kv_off.  cache [pages, 1, page, C + R]; q_plain [H, head_rows, D] of the cache's type; q_rot float32 [H, head_rows, R].
-int infero_latent_prepare(const float* proj, int proj_stride, int q_off, int kv_off, const float* norm_w, float eps,
+// proj float32 [T, proj_stride]: the C + R columns of the latent row from kv_off.  q_src float32 [T, q_stride]: the
+// query's H * (D + R) columns from q_off (the same array as proj where one product gives both, another where the queries
+// come from a product of their own).  cache [pages, 1, page, C + R]; q_plain [H, head_rows, D] of the cache's type; q_rot
+// float32 [H, head_rows, R] (R may be 0: no rotated part).
+int infero_latent_prepare_from(const float* proj, int proj_stride, const float* q_src, int q_stride, int q_off, int kv_off,
+                               const float* norm_w, float eps,
                           const double* freq, int rot, int pairing, float amp, const int* positions, const int* tok_entry,
                           const int* block_table, int max_blocks, int page_size, void* cache, int dtype, int write_cache,
                           void* q_plain, float* q_rot, long long head_rows, int n_tokens, int H, int D, int R, int C,
@@ -190,14 +194,24 @@ int infero_latent_prepare(const float* proj, int proj_stride, int q_off, int kv_
     const int heads_per_block = n_tokens >= 512 ? H : max(1, H / 8);
     const dim3 grid(n_tokens, 1 + (H + heads_per_block - 1) / heads_per_block);
     if (dtype == INFERO_F32)
-        latent_prepare_kernel<float><<<grid, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_off, kv_off, norm_w, eps, freq,
+        latent_prepare_kernel<float><<<grid, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_src, q_stride, q_off, kv_off, norm_w, eps, freq,
             rot, pairing, amp, positions, tok_entry, block_table, max_blocks, page_size, (float*)cache, write_cache,
             (float*)q_plain, q_rot, head_rows, H, D, R, C, heads_per_block);
     else
-        latent_prepare_kernel<bf16><<<grid, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_off, kv_off, norm_w, eps, freq,
+        latent_prepare_kernel<bf16><<<grid, PREP_THREADS, 0, stream>>>(proj, proj_stride, q_src, q_stride, q_off, kv_off, norm_w, eps, freq,
             rot, pairing, amp, positions, tok_entry, block_table, max_blocks, page_size, (bf16*)cache, write_cache,
             (bf16*)q_plain, q_rot, head_rows, H, D, R, C, heads_per_block);
     return infero_check_launch("latent_prepare");
+}
+
+int infero_latent_prepare(const float* proj, int proj_stride, int q_off, int kv_off, const float* norm_w, float eps,
+                          const double* freq, int rot, int pairing, float amp, const int* positions, const int* tok_entry,
+                          const int* block_table, int max_blocks, int page_size, void* cache, int dtype, int write_cache,
+                          void* q_plain, float* q_rot, long long head_rows, int n_tokens, int H, int D, int R, int C,
+                          cudaStream_t stream) {
+    return infero_latent_prepare_from(proj, proj_stride, proj, proj_stride, q_off, kv_off, norm_w, eps, freq, rot, pairing, amp,
+                                      positions, tok_entry, block_table, max_blocks, page_size, cache, dtype, write_cache,
+                                      q_plain, q_rot, head_rows, n_tokens, H, D, R, C, stream);
 }
 
 // q_lat float32 [H, head_rows, C] (the plain query parts carried through Wuk^T), q_rot float32 [H, head_rows, R];

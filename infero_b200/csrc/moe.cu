@@ -9,6 +9,11 @@
 //   down: y[t, i] = sum_c weight[t, c] * (Wd_e[i] . act[t, c]) (+ gate_t * shared[t, i]); one warp per i,
 //         choices added in ascending c, so a token's result does not depend on the batch.
 // Expert weights are stacked: gate_up [E, 2 ff, d] with rows alternating gate_j, up_j; down [E, d, ff].
+//
+// select by scores: every expert's score is the sigmoid of its logit; the `top` largest scores are chosen (lowest index
+//   wins a tie); the weights are the chosen scores, divided by their sum where asked.
+// ungated experts (up [E, ff, d]): act[t, c, j] = f(w * (Wu_e[j] . h_t)) with f the squared relu and w the pair's weight
+//   where the weight multiplies what the expert reads (then the down stage adds the choices up unweighted), else 1.
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -83,6 +88,46 @@ moe_select_kernel(const float* __restrict__ logits, int stride, int gate_col, in
     if (lane < top) {
         top_idx[(size_t)t * top + lane] = mine_e;
         top_w[(size_t)t * top + lane] = mine / sum;
+    }
+}
+
+// Scores are sigmoid(logit); the `top` largest are chosen by score (ties: the lower index); weights are the scores,
+// divided by the sum of the chosen ones where `renorm`.  One warp per token.
+__global__ void __launch_bounds__(RWARPS * 32)
+moe_select_scored_kernel(const float* __restrict__ logits, int stride, int* __restrict__ top_idx,
+                         float* __restrict__ top_w, int n_tokens, int E, int top, int renorm) {
+    __shared__ float sc[RWARPS][MAX_E];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * RWARPS + warp;
+    if (t >= n_tokens) return;
+    const float* zr = logits + (size_t)t * stride;
+    for (int e = lane; e < E; e += 32) sc[warp][e] = 1.0f / (1.0f + expf(-zr[e]));
+    __syncwarp();
+    float mine = 0.f, sum = 0.f;
+    int mine_e = 0;
+    for (int c = 0; c < top; ++c) {
+        float best = -CUDART_INF_F;
+        int be = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[warp][e];
+            if (v > best) best = v, be = e;               // ascending e: the lowest index of equal values stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > best || (ov == best && oe < be)) best = ov, be = oe;
+        }
+        if (be == 0x7fffffff) be = 0, best = 0.f;         // nothing left to pick (scores that are no numbers)
+        sum += best;
+        if (lane == c) mine = best, mine_e = be;
+        __syncwarp();
+        if (lane == 0) sc[warp][be] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    if (lane < top) {
+        top_idx[(size_t)t * top + lane] = mine_e;
+        top_w[(size_t)t * top + lane] = renorm ? mine / (sum + 1e-20f) : mine;
     }
 }
 
@@ -188,6 +233,23 @@ moe_up_kernel(const T* __restrict__ h, int h_stride, const T* __restrict__ gate_
     if (lane == 0) act[(size_t)item * ff + j] = from_f32<T>(glu_act(g, u, act_kind, act_limit, act_alpha));
 }
 
+// Ungated experts: up [E, ff, d]; in_w (or null) multiplies the product before the squared relu.
+template <typename T>
+__global__ void __launch_bounds__(EWARPS * 32)
+moe_up_plain_kernel(const T* __restrict__ h, int h_stride, const T* __restrict__ up, const int* __restrict__ top_idx,
+                    const float* __restrict__ in_w, T* __restrict__ act, int d, int ff, int top) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.y;                              // token * top + choice
+    const int t = item / top;
+    const int j = blockIdx.x * EWARPS + warp;
+    if (j >= ff) return;
+    const int e = top_idx[item];
+    float v = warp_dot(up + ((size_t)e * ff + j) * d, h + (size_t)t * h_stride, d, lane);
+    if (in_w) v *= in_w[item];
+    v = fmaxf(v, 0.f);
+    if (lane == 0) act[(size_t)item * ff + j] = from_f32<T>(v * v);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(EWARPS * 32)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ top_idx,
@@ -201,7 +263,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int
     for (int c = 0; c < top; ++c) {
         const int e = top_idx[(size_t)t * top + c];
         const float v = warp_dot(down + ((size_t)e * d + i) * ff, act + ((size_t)t * top + c) * ff, ff, lane);
-        acc = fmaf(top_w[(size_t)t * top + c], v, acc);
+        acc = top_w ? fmaf(top_w[(size_t)t * top + c], v, acc) : acc + v;
     }
     if (lane == 0) {
         if (shared) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared[(size_t)t * d + i], acc);
@@ -233,6 +295,40 @@ int infero_moe_select_grouped(const float* logits, int stride, const float* corr
     moe_select_grouped_kernel<<<(n_tokens + RWARPS - 1) / RWARPS, RWARPS * 32, 0, stream>>>(
         logits, stride, correction, top_idx, top_w, n_tokens, E, top, n_groups, keep);
     return infero_check_launch("moe_select_grouped");
+}
+
+int infero_moe_select_scored(const float* logits, int stride, int* top_idx, float* top_w, int n_tokens, int E, int top,
+                             int renorm, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(E >= 1 && E <= MAX_E && top >= 1 && top <= E && top <= MAX_TOP,
+                   "moe select: %d experts (at most %d), top %d (at most %d)", E, MAX_E, top, MAX_TOP);
+    moe_select_scored_kernel<<<(n_tokens + RWARPS - 1) / RWARPS, RWARPS * 32, 0, stream>>>(logits, stride, top_idx, top_w,
+                                                                                         n_tokens, E, top, renorm);
+    return infero_check_launch("moe_select_scored");
+}
+
+// Ungated experts with the squared relu: up [E, ff, d], down [E, d, ff].  weight_input: the pair's weight multiplies what
+// the expert reads and the choices are added up as they are; else it multiplies the expert's result.
+int infero_moe_experts_plain_streamed(const void* h, int h_stride, const void* up, const void* down, int dtype,
+                                      const int* top_idx, const float* top_w, int weight_input, const float* shared,
+                                      void* act, float* y, int n_tokens, int d, int ff, int top, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(n_tokens * (long long)top <= 65535 && n_tokens <= 65535, "moe: %d tokens are too many for the streaming path", n_tokens);
+    const dim3 gu((ff + EWARPS - 1) / EWARPS, n_tokens * top), gd((d + EWARPS - 1) / EWARPS, n_tokens);
+    const float* in_w = weight_input ? top_w : nullptr;
+    const float* out_w = weight_input ? nullptr : top_w;
+    if (dtype == INFERO_F32) {
+        moe_up_plain_kernel<float><<<gu, EWARPS * 32, 0, stream>>>((const float*)h, h_stride, (const float*)up, top_idx, in_w,
+                                                                  (float*)act, d, ff, top);
+        moe_down_kernel<float><<<gd, EWARPS * 32, 0, stream>>>((const float*)act, (const float*)down, top_idx, out_w, shared,
+                                                              nullptr, y, d, ff, top);
+    } else {
+        moe_up_plain_kernel<bf16><<<gu, EWARPS * 32, 0, stream>>>((const bf16*)h, h_stride, (const bf16*)up, top_idx, in_w,
+                                                                 (bf16*)act, d, ff, top);
+        moe_down_kernel<bf16><<<gd, EWARPS * 32, 0, stream>>>((const bf16*)act, (const bf16*)down, top_idx, out_w, shared,
+                                                             nullptr, y, d, ff, top);
+    }
+    return infero_check_launch("moe_experts_plain_streamed");
 }
 
 // act: [tokens * top, ff] of dtype (scratch); y float32 [tokens, d]; shared float32 [tokens, d] or null.

@@ -65,14 +65,27 @@ __global__ void moe_align_kernel(const int* __restrict__ top_idx, int n_pairs, i
     }
 }
 
-// xs[r, :] = h[a_rows[r], :] (zeros where a_rows[r] < 0); rows of d bf16, d a multiple of 8
+// xs[r, :] = h[a_rows[r], :] (zeros where a_rows[r] < 0); rows of d bf16, d a multiple of 8.  With pair_w the row is
+// multiplied by the weight of the pair it stands for (pair_w[sorted_pair[r]]) and rounded once.
 __global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, int h_stride, const int* __restrict__ a_rows,
-                                       bf16* __restrict__ xs, int d) {
+                                       bf16* __restrict__ xs, int d, const int* __restrict__ sorted_pair,
+                                       const float* __restrict__ pair_w) {
     const size_t r = blockIdx.x;
     const int src = a_rows[r];
+    const float f = (pair_w && src >= 0) ? pair_w[sorted_pair[r]] : 1.0f;
     for (int c = threadIdx.x; c < d / 8; c += blockDim.x) {
         uint4 v = make_uint4(0, 0, 0, 0);
         if (src >= 0) v = *reinterpret_cast<const uint4*>(h + (size_t)src * h_stride + c * 8);
+        if (pair_w) {
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+                const __nv_bfloat162 p2 = __floats2bfloat162_rn(lo * f, hi * f);
+                w[j] = *reinterpret_cast<const uint32_t*>(&p2);
+            }
+            v = make_uint4(w[0], w[1], w[2], w[3]);
+        }
         *reinterpret_cast<uint4*>(xs + r * d + c * 8) = v;
     }
 }
@@ -84,7 +97,10 @@ __global__ void moe_combine_rows_kernel(const float* __restrict__ rows, const in
     const size_t t = blockIdx.x;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float acc = 0.f;
-        for (int c = 0; c < top; ++c) acc = fmaf(top_w[t * top + c], rows[(size_t)pair_row[t * top + c] * d + i], acc);
+        for (int c = 0; c < top; ++c) {
+            const float v = rows[(size_t)pair_row[t * top + c] * d + i];
+            acc = top_w ? fmaf(top_w[t * top + c], v, acc) : acc + v;
+        }
         if (shared) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared[t * d + i], acc);
         y[t * d + i] = acc;
     }
@@ -263,15 +279,23 @@ int infero_moe_tc_tiles(int n_pairs, int E) { return (n_pairs + E * 127 + 127) /
 
 // sorted_pair, a_rows int32 [tiles * 128]; tile_expert int32 [tiles + 1]; pair_row int32 [tokens * top];
 // xs bf16 [tiles * 128, d]: the tokens' rows in sorted order.
-int infero_moe_tc_prepare(const void* h, int h_stride, const int* top_idx, int* sorted_pair, int* a_rows, int* tile_expert,
-                          int* pair_row, void* xs, int n_tokens, int d, int E, int top, cudaStream_t stream) {
+// pair_w (float32 [tokens * top] or null): a row of xs is its token's row times the weight of its pair.
+int infero_moe_tc_prepare_scaled(const void* h, int h_stride, const int* top_idx, int* sorted_pair, int* a_rows,
+                                 int* tile_expert, int* pair_row, void* xs, int n_tokens, int d, int E, int top,
+                                 const float* pair_w, cudaStream_t stream) {
     INFERO_REQUIRE(d % 8 == 0 && h_stride % 8 == 0, "moe: width %d must be a multiple of 8", d);
     const int n_pairs = n_tokens * top, tiles = infero_moe_tc_tiles(n_pairs, E);
     const size_t sh = (size_t)(3 * E + 1) * sizeof(int);
     INFERO_REQUIRE(sh <= 48 * 1024, "moe grouped: %d experts are too many", E);
     moe_align_kernel<<<1, 1024, sh, stream>>>(top_idx, n_pairs, E, top, sorted_pair, tile_expert, tiles, a_rows, 128, pair_row);
-    moe_gather_rows_kernel<<<tiles * 128, 128, 0, stream>>>((const bf16*)h, h_stride, a_rows, (bf16*)xs, d);
+    moe_gather_rows_kernel<<<tiles * 128, 128, 0, stream>>>((const bf16*)h, h_stride, a_rows, (bf16*)xs, d, sorted_pair, pair_w);
     return infero_check_launch("moe_tc_prepare");
+}
+
+int infero_moe_tc_prepare(const void* h, int h_stride, const int* top_idx, int* sorted_pair, int* a_rows, int* tile_expert,
+                          int* pair_row, void* xs, int n_tokens, int d, int E, int top, cudaStream_t stream) {
+    return infero_moe_tc_prepare_scaled(h, h_stride, top_idx, sorted_pair, a_rows, tile_expert, pair_row, xs, n_tokens, d, E,
+                                        top, nullptr, stream);
 }
 
 int infero_moe_tc_combine(const float* rows, const int* pair_row, const float* top_w, const float* shared,

@@ -5,6 +5,8 @@
 //   norm 1: RMS norm over the whole query projection (all heads at once) with a weight per coordinate, and likewise
 //           over the whole key projection, before the rotation
 //   norm 2: every head of q and k divided by its root mean square (no weight), after the rotation
+//   norm 3: an RMS norm over every head of q and of k with a weight of D numbers shared by the heads (one for q, one
+//           for k), before the rotation
 //
 //   rotation: the first `rot` coordinates of every head, coordinate i with i + rot/2, by position * freq[i]; the angle
 //   is formed in 64-bit from a 64-bit table made on the host (any scaling of the frequencies is the host's) and brought
@@ -86,6 +88,18 @@ qk_prepare_kernel(const float* __restrict__ proj, int proj_stride, int q_off, in
         for (int i = tid; i < nq; i += THREADS) buf[i] = buf[i] * rq * load_any(q_norm_w, norm_w_dtype, i);
         for (int i = tid; i < nk; i += THREADS) buf[nq + i] = buf[nq + i] * rk * load_any(k_norm_w, norm_w_dtype, i);
     }
+    if (norm_mode == 3) {
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int head = warp; head < H + Gk; head += THREADS / 32) {
+            float* hp = buf + (size_t)head * D;
+            const void* w = head < H ? q_norm_w : k_norm_w;
+            float s = 0.f;
+            for (int i = lane; i < D; i += 32) s = fmaf(hp[i], hp[i], s);
+            s = warp_sum(s);
+            const float r = 1.0f / sqrtf(s / (float)D + eps);
+            for (int i = lane; i < D; i += 32) hp[i] = hp[i] * r * load_any(w, norm_w_dtype, i);
+        }
+    }
     __syncthreads();
     // rotation: a thread owns a pair, so nothing is read after it was rewritten
     for (int e = tid; e < (H + Gk) * half; e += THREADS) {
@@ -159,8 +173,8 @@ int infero_qk_prepare(const float* proj, int proj_stride, int q_off, int k_off, 
                       int write_cache, int n_tokens, int H, int G, int D, int V, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D, "qk_prepare: %d rotated coordinates of %d", rot, D);
-    INFERO_REQUIRE(norm_mode >= 0 && norm_mode <= 2, "qk_prepare: norm mode %d", norm_mode);
-    INFERO_REQUIRE(norm_mode != 1 || (q_norm_w && (!write_cache || k_norm_w)), "qk_prepare: norm weights missing");
+    INFERO_REQUIRE(norm_mode >= 0 && norm_mode <= 3, "qk_prepare: norm mode %d", norm_mode);
+    INFERO_REQUIRE((norm_mode != 1 && norm_mode != 3) || (q_norm_w && (!write_cache || k_norm_w)), "qk_prepare: norm weights missing");
     INFERO_REQUIRE(v_off >= 0 || V == D || !write_cache, "qk_prepare: values taken from keys need equal widths (%d, %d)", V, D);
     const size_t smem = ((size_t)(H + (write_cache ? G : 0)) * D + rot) * sizeof(float);
     INFERO_REQUIRE(smem <= 200 * 1024, "qk_prepare: %d heads of %d do not fit in shared memory", H + G, D);

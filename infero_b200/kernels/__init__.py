@@ -270,18 +270,21 @@ def rope_cache_partials(qkv: Partials, q_out: torch.Tensor, positions: torch.Ten
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_table: torch.Tensor, tok_entry: torch.Tensor, positions: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
-                      scale: float, value_dim: int = 0, sink: bool = False) -> None:
+                      scale: float, value_dim: int = 0, sink: bool = False,
+                      slopes: Optional[torch.Tensor] = None) -> None:
     """q: [T, >= H*D] view (row stride free), out [T, H*V] with V = ``value_dim`` (0: the keys' width).  ``sink``: one
-    more term exp(0) in the softmax's sum, without a value."""
+    more term exp(0) in the softmax's sum, without a value.  ``slopes`` float32 [H]: head h's score loses slopes[h]
+    times the distance between the query and the key."""
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
-    _check(lib().infero_attention_generic_ex(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.is_contiguous() and slopes.numel() == n_heads)
+    _check(lib().infero_attention_generic_bias(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
                                              _ptr(k_cache), _ptr(v_cache), c_int(_dt(q)),
                                              _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]),
                                              _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),
                                              c_int(T), c_int(n_heads), c_int(n_kv), c_int(head_dim),
                                              c_int(value_dim or head_dim), c_int(page_size), c_int(window or 0),
-                                             c_float(scale), c_int(1 if sink else 0), _stream()))
+                                             c_float(scale), c_int(1 if sink else 0), _ptr(slopes), _stream()))
 
 
 # ---- sampling --------------------------------------------------------------------------------

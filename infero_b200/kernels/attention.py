@@ -203,13 +203,27 @@ def _batch_shape(ctx):
     return memo
 
 
-def paged_attention_ex(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, sink: bool) -> None:
+def paged_attention_ex(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, sink: bool,
+                       slopes=None) -> None:
     """Attention with values of their own width and, optionally, a sink (one more term exp(0) in the softmax's sum, without
-    a value).  q [T, H*D] rotated queries; out [T, H*V].  Equal widths take the same kernels as ``paged_attention``
-    (the sink is a term added to the sum where a row's result is divided by it); values of another width than the keys
-    run on the any-type kernel."""
+    a value) or a distance bias (``slopes`` float32 [H]: head h's score loses slopes[h] times the distance to the key).
+    q [T, H*D] rotated queries; out [T, H*V].  Equal widths take the same kernels as ``paged_attention`` (the sink is a
+    term added to the sum where a row's result is divided by it); values of another width than the keys, and scores
+    with a distance bias where the tensor-core kernels have no instance for it, run on the any-type kernel."""
+    if slopes is not None:
+        if biased_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, slopes):
+            return
+        attention_generic(q, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim, kv.page_size,
+                          window, scale, value_dim=value_dim, sink=sink, slopes=slopes)
+        return
     if value_dim == head_dim:
         paged_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, window, scale, sink=sink)
         return
     attention_generic(q, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim, kv.page_size,
                       window, scale, value_dim=value_dim, sink=sink)
+
+
+def biased_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, slopes) -> bool:
+    """Attention with a distance bias on a tensor-core kernel; False, with nothing launched, where there is none for
+    these sizes and this element type."""
+    return False

@@ -19,18 +19,22 @@ TILE = 128
 def prepare(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Tensor, eps: float, freq: Optional[torch.Tensor],
             pairing: str, amp: float, positions, tok_entry, block_table, cache: torch.Tensor, page_size: int,
             q_plain: torch.Tensor, q_rot: torch.Tensor, n_tokens: int, H: int, D: int, R: int, C: int,
-            write_cache: bool = True) -> None:
+            write_cache: bool = True, q_src: Optional[torch.Tensor] = None) -> None:
     """From the input product (float32 [T, >= ...]): the normed latent and the rotated key part go to the token's
     page, the plain query parts to q_plain [H, rows, D], the rotated ones to q_rot float32 [H, rows, R].  ``freq``: the
-    rotary table in float64 (the angle is formed in 64-bit)."""
+    rotary table in float64 (the angle is formed in 64-bit).  ``q_src`` (float32 [T, >= q_off + H (D + R)]): the
+    queries come from this array instead of ``proj`` (a product of their own)."""
+    if q_src is None:
+        q_src = proj
+    assert q_src.dtype == torch.float32 and q_src.stride(1) == 1 and q_src.shape[0] == proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == C + R
     assert cache.shape[1] == 1 and q_plain.dtype == cache.dtype and q_plain.is_contiguous() and q_rot.dtype == torch.float32
     rows = q_plain.shape[1]
     assert tuple(q_plain.shape) == (H, rows, D) and tuple(q_rot.shape) == (H, rows, R) and q_rot.is_contiguous()
     assert freq is None or (freq.dtype == torch.float64 and freq.is_contiguous())
     rot = 0 if freq is None else 2 * freq.numel()
-    _check(lib().infero_latent_prepare(
-        _ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(kv_off), _ptr(_f32(norm_w, "norm_w")), c_float(eps),
+    _check(lib().infero_latent_prepare_from(
+        _ptr(proj), c_int(proj.stride(0)), _ptr(q_src), c_int(q_src.stride(0)), c_int(q_off), c_int(kv_off), _ptr(_f32(norm_w, "norm_w")), c_float(eps),
         _ptr(freq), c_int(rot), c_int(1 if pairing == "adjacent" else 0), c_float(amp),
         _ptr(_i32(positions, "positions")), _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(block_table, "block_table")),
         c_int(block_table.shape[1]), c_int(page_size), _ptr(cache), c_int(_dt(cache)), c_int(1 if write_cache else 0),

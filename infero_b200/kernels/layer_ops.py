@@ -341,7 +341,8 @@ def qk_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, norm_mode
     """From the 32-bit product row of every token (``proj`` [T, >= ...], columns ``q_off`` / ``k_off`` / ``v_off``; a
     negative ``v_off``: the values are the keys as projected) to normed, rotated queries in ``q_out`` [T, H*D] and keys and
     values in the token's page.  ``norm_mode`` 0 none, 1 weighted RMS over the whole projection before the rotation,
-    2 unit RMS per head after it.  ``freq64`` float64 [rot/2] (None: no rotation), ``amp`` multiplies cos and sin."""
+    2 unit RMS per head after it, 3 weighted RMS per head before it (weights of D numbers shared by the heads).
+    ``freq64`` float64 [rot/2] (None: no rotation), ``amp`` multiplies cos and sin."""
     T = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.shape == (T, H * D)
     rot = 0
@@ -353,6 +354,9 @@ def qk_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, norm_mode
         assert k_cache.shape[1:] == (G, page_size, D) and v_cache.shape[1:] == (G, page_size, V)
     if norm_mode == 1:
         assert q_norm_w.numel() == H * D and (not write_cache or k_norm_w.numel() == G * D)
+        assert k_norm_w is None or k_norm_w.dtype == q_norm_w.dtype
+    if norm_mode == 3:
+        assert q_norm_w.numel() == D and (not write_cache or k_norm_w.numel() == D)
         assert k_norm_w is None or k_norm_w.dtype == q_norm_w.dtype
     _check(lib().infero_qk_prepare(
         _ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), c_int(norm_mode), _ptr(q_norm_w),
@@ -435,3 +439,117 @@ def rglru(proj: torch.Tensor, y_off: int, x_off: int, conv_w: torch.Tensor, conv
                                _ptr(_i32(entry_q_len, "entry_q_len")), _ptr(_i32(entry_slot, "entry_slot")), _ptr(out),
                                c_int(out.stride(0)), c_int(_dt(out)),
                                c_int(n_entries), c_int(C), c_int(blocks), c_int(max(1, int(max_q_len))), c_float(scale), _stream()))
+
+
+# ---- state-space recurrence (csrc/ssd.cu), gated group norm ---------------------------------------------------------
+def ssd_state_floats(heads: int, N: int, P: int, groups: int, taps: int) -> int:
+    """Floats of one request's state: the convolution's last taps - 1 inputs, then S [heads, N, P]."""
+    return (taps - 1) * (heads * P + 2 * groups * N) + heads * N * P
+
+
+def ssd(proj: torch.Tensor, z_off: int, x_off: int, dt_off: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor],
+        dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor, norm_w: torch.Tensor, eps: float, norm_groups: int,
+        state: torch.Tensor, tok_entry, entry_q_start, entry_q_len, entry_slot, n_entries: int, out: torch.Tensor,
+        heads: int, groups: int, N: int, P: int, scale: float = 1.0, max_q_len: int = 1) -> None:
+    """The state-space recurrence of every request of the step over its new tokens, and the gated, grouped norm of its
+    result; see csrc/ssd.cu.  ``proj`` float32 [T, >= ...] holds [z | x B C | dt] at ``z_off`` / ``x_off`` / ``dt_off``;
+    ``conv_w`` float32 [CH, taps] over the CH = heads P + 2 groups N channels of [x | B | C]; ``state`` float32
+    [slots, floats] (``ssd_state_floats``); ``out`` [T, heads * P] (a column slice allowed) receives
+    rms_parts(y * silu(z)) * norm_w * scale.  ``max_q_len``: the longest portion of the step."""
+    from .tc_gemm import sm_count
+    T = proj.shape[0]
+    CH, taps = conv_w.shape
+    inner = heads * P
+    assert CH == inner + 2 * groups * N and proj.dtype == torch.float32 and proj.stride(1) == 1
+    assert out.shape == (T, inner) and out.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == ssd_state_floats(heads, N, P, groups, taps)
+    _f32(conv_w, "conv_w"), _f32(conv_b, "conv_b"), _f32(dt_bias, "dt_bias"), _f32(a_log, "a_log"), _f32(skip, "skip"), _f32(norm_w, "norm_w")
+    dev = proj.device
+    L = lib()
+    u = torch.empty((T, CH), dtype=torch.float32, device=dev)
+    qs, ql, sl = _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")), _ptr(_i32(entry_slot, "entry_slot"))
+    _check(L.infero_ssd_conv(_ptr(proj), c_int(proj.stride(0)), c_int(x_off), _ptr(conv_w), _ptr(conv_b), c_int(taps), _ptr(state),
+                             c_longlong(state.stride(0)), _ptr(_i32(tok_entry, "tok_entry")), qs, ql, sl, _ptr(u), c_int(T),
+                             c_int(n_entries), c_int(CH), _stream()))
+    y = torch.empty((T, inner), dtype=torch.float32, device=dev)
+    L.infero_ssd_scan_scratch.restype = c_longlong
+    need = int(L.infero_ssd_scan_scratch(c_int(n_entries), c_int(int(max_q_len)), c_int(heads), c_int(N), c_int(P)))
+    scratch = torch.empty(need, dtype=torch.float32, device=dev) if need else None
+    _check(L.infero_ssd_scan(_ptr(u), _ptr(proj), c_int(proj.stride(0)), c_int(dt_off), _ptr(dt_bias), _ptr(a_log), _ptr(skip),
+                             _ptr(state), c_longlong(state.stride(0)), c_int(taps), qs, ql, sl, _ptr(y), c_int(n_entries),
+                             c_int(max(1, int(max_q_len))), c_int(heads), c_int(groups), c_int(N), c_int(P), _ptr(scratch),
+                             c_int(sm_count(dev)), _stream()))
+    gated_group_norm(y, proj[:, z_off:z_off + inner], norm_w, eps, norm_groups, out, scale)
+
+
+def gated_group_norm(y: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, eps: float, parts: int,
+                     out: torch.Tensor, scale: float = 1.0) -> None:
+    """out = v / sqrt(mean over each of ``parts`` equal parts of v^2 + eps) * weight * scale with v = y * silu(gate)
+    (v = y without a gate).  y, gate float32 [T, n] (column slices allowed); out [T, n] of any element type."""
+    T, n = y.shape
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and out.shape == (T, n) and out.stride(1) == 1
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == (T, n) and gate.stride(1) == 1)
+    assert weight.numel() == n
+    _check(lib().infero_gated_group_norm(_ptr(y), c_int(y.stride(0)), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
+                                         _ptr(_f32(weight, "weight")), c_float(eps), c_float(scale), _ptr(out),
+                                         c_int(out.stride(0)), c_int(_dt(out)), c_int(T), c_int(n), c_int(parts), _stream()))
+
+
+# ---- experts chosen by scores, ungated experts (csrc/moe.cu, csrc/moe_grouped.cu) -----------------------------------
+def moe_select_scored(logits: torch.Tensor, E: int, top: int, renorm: bool = False):
+    """From float32 logits [T, >= E]: scores sigmoid(logit); the ``top`` largest (lowest index wins a tie);
+    (top_idx int32 [T, top], top_w float32 [T, top]) with top_w the chosen scores, over their sum where ``renorm``."""
+    T = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= E
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(lib().infero_moe_select_scored(_ptr(logits), c_int(logits.stride(0)), _ptr(idx), _ptr(w), c_int(T), c_int(E),
+                                          c_int(top), c_int(1 if renorm else 0), _stream()))
+    return idx, w
+
+
+def moe_plain_streamed(h, up, down, top_idx, top_w, weight_input: bool, shared, y) -> None:
+    """y[t] = sum_c expert_c(w_c h[t]) (``weight_input``) or sum_c w_c expert_c(h[t]), expert = down(relu(up x)^2),
+    (+ shared[t]); every (token, choice) streams its expert's rows.  up [E, ff, d], down [E, d, ff]."""
+    T, d = h.shape
+    E, ff, _ = up.shape
+    top = top_idx.shape[1]
+    assert up.dtype == h.dtype == down.dtype and up.is_contiguous() and down.is_contiguous() and h.stride(1) == 1
+    assert tuple(down.shape) == (E, d, ff) and y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d)
+    scratch = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    _check(lib().infero_moe_experts_plain_streamed(_ptr(h), c_int(h.stride(0)), _ptr(up), _ptr(down), c_int(_dt(h)),
+                                                   _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
+                                                   c_int(1 if weight_input else 0), _ptr(_f32(shared, "shared")),
+                                                   _ptr(scratch), _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(top), _stream()))
+
+
+def moe_plain_tc(h, up, down, top_idx, top_w, weight_input: bool, shared, y) -> None:
+    """The same result by grouped products on the tcgen05 kernel (bf16): the tokens' rows are copied into expert order
+    in tiles of 128 rows, times their pair's weight where it multiplies the expert's input; the first grouped product
+    applies the squared relu in its epilogue; the rows of a token's choices are added up in ascending order."""
+    from .tc_gemm import sm_count
+    T, d = h.shape
+    E, ff, _ = up.shape
+    top = top_idx.shape[1]
+    assert h.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and down.dtype == torch.bfloat16
+    assert up.is_contiguous() and down.is_contiguous() and tuple(down.shape) == (E, d, ff)
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (T, d) and h.stride(1) == 1
+    L = lib()
+    tiles = int(L.infero_moe_tc_tiles(c_int(T * top), c_int(E)))
+    R, dev = tiles * 128, h.device
+    ints = torch.empty(2 * R + tiles + 1 + T * top, dtype=torch.int32, device=dev)
+    sorted_pair, a_rows, tile_expert, pair_row = ints[:R], ints[R:2 * R], ints[2 * R:2 * R + tiles + 1], ints[2 * R + tiles + 1:]
+    xs = torch.empty((R, d), dtype=torch.bfloat16, device=dev)
+    _f32(top_w, "top_w")
+    _check(L.infero_moe_tc_prepare_scaled(_ptr(h), c_int(h.stride(0)), _ptr(_i32(top_idx, "top_idx")), _ptr(sorted_pair),
+                                          _ptr(a_rows), _ptr(tile_expert), _ptr(pair_row), _ptr(xs), c_int(T), c_int(d),
+                                          c_int(E), c_int(top), _ptr(top_w if weight_input else None), _stream()))
+    act = torch.empty((R, ff), dtype=torch.bfloat16, device=dev)
+    sms = sm_count(dev)
+    _check(L.infero_gemm_tc_grouped(_ptr(xs), _ptr(up), _ptr(act), c_int(2), c_int(R), c_int(ff), c_int(d), c_int(d),
+                                    c_int(ff), _ptr(tile_expert), c_int(E), c_int(sms), *_act_args(None), _stream()))
+    rows = torch.empty((R, d), dtype=torch.float32, device=dev)
+    _check(L.infero_gemm_tc_grouped(_ptr(act), _ptr(down), _ptr(rows), c_int(0), c_int(R), c_int(d), c_int(ff), c_int(ff),
+                                    c_int(d), _ptr(tile_expert), c_int(E), c_int(sms), *_act_args(None), _stream()))
+    _check(L.infero_moe_tc_combine(_ptr(rows), _ptr(pair_row), _ptr(None if weight_input else top_w), _ptr(_f32(shared, "shared")),
+                                   _ptr(None), _ptr(y), c_int(T), c_int(d), c_int(top), _stream()))

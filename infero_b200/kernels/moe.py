@@ -38,3 +38,22 @@ def experts(h, gate_up, down, top_idx, top_w, shared, shared_gate, y, act=None) 
         L.moe_experts_streamed(h[a:b], gate_up, down, top_idx[a:b], top_w[a:b],
                                None if shared is None else shared[a:b], None if shared_gate is None else shared_gate[a:b],
                                y[a:b], act)
+
+
+def plain_experts(h, up, down, top_idx, top_w, weight_input: bool, shared, y) -> None:
+    """Ungated experts down(relu(up x)^2), up [E, ff, d], down [E, d, ff]: y[t] = sum_c expert_c(w_c h[t]) where the
+    weight multiplies the expert's input (``weight_input``), else sum_c w_c expert_c(h[t]); ``shared`` float32 [T, d]
+    or None is added.  More pairs than experts on the bf16 path: grouped tcgen05 products; else every pair streams its
+    expert."""
+    T, d = h.shape
+    E, ff, _ = up.shape
+    top = top_idx.shape[1]
+    if (h.dtype == torch.bfloat16 and T >= GROUPED_FROM and T * top > E and d % 8 == 0 and ff % 8 == 0
+            and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0 and up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0):
+        L.moe_plain_tc(h, up, down, top_idx, top_w, weight_input, shared, y)
+        return
+    step = max(1, 65535 // top)
+    for a in range(0, T, step):
+        b = min(T, a + step)
+        L.moe_plain_streamed(h[a:b], up, down, top_idx[a:b], top_w[a:b], weight_input,
+                             None if shared is None else shared[a:b], y[a:b])

@@ -9,10 +9,11 @@ from .mlp import GluMlp, Relu2Mlp, SwiGluMlp
 from .attention import GqaAttention
 from .hgrn2 import Hgrn2Mixer
 from .diff_attention import DiffAttention
-from .moe import GroupedMoe, MoeSwiGlu
+from .moe import GroupedMoe, MoeSwiGlu, ScoredMoe
 from .latent_attention import LatentAttention
 from .normed_attention import NormedAttention
 from .rglru import RgLruMixer
+from .ssd import SsdMixer
 from .parallel import ParallelMixer
 from .block import GatedPostNormBlock, HyperPreNormBlock, PreNormBlock
 
@@ -36,8 +37,10 @@ register_part("block", "hyper_prenorm", HyperPreNormBlock)
 register_part("mixer", "normed_attention", NormedAttention)
 register_part("mixer", "rglru", RgLruMixer)
 register_part("mixer", "parallel", ParallelMixer)
+register_part("mixer", "ssd", SsdMixer)
+register_part("feed_forward", "moe_scored", ScoredMoe)
 
 __all__ = ["FeedForward", "KvCacheSpec", "Mixer", "Norm", "Part", "PositionEncoding", "StateSpec",
            "TensorDecl", "Linear", "RmsNorm", "ScalarRmsNorm", "RopeNeox", "RopeInterleaved", "SwiGluMlp", "GqaAttention",
            "Hgrn2Mixer", "DiffAttention", "MoeSwiGlu", "PreNormBlock", "GatedPostNormBlock", "LayerNorm", "GluMlp", "Relu2Mlp",
-           "GroupedMoe", "LatentAttention", "HyperPreNormBlock", "NormedAttention", "RgLruMixer", "ParallelMixer"]
+           "GroupedMoe", "LatentAttention", "HyperPreNormBlock", "NormedAttention", "RgLruMixer", "ParallelMixer", "SsdMixer", "ScoredMoe"]

@@ -25,13 +25,18 @@ class LatentAttention(Mixer):
         ->  per-head product with Wuk^T  ->  attention over latent rows  ->  per-head product with Wuv
         ->  finish (gate, heads side by side)  ->  output product.
 
-    Rotation: the position part's table (with any stretching of the frequencies and its amplitude) and pairing."""
+    Rotation: the position part's table (with any stretching of the frequencies and its amplitude) and pairing; R may
+    be 0 (no rotated part: positions enter through the causal mask alone).
+
+    ``q_latent_dim`` = Q > 0: the queries have a latent of their own.  The stacked product gives [dq | down (| gate)], the
+    first Q columns are RMS-normed with a weight (32-bit) and a second product with Wuq [H (D + R), Q] gives the queries."""
 
     def __init__(self, spec: MixerSpec, prefix: str):
         self.spec, self.prefix = spec, prefix
         self.H, self.D, self.R, self.V, self.C = spec.num_heads, spec.head_dim, spec.rot_dim, spec.v_dim, spec.latent_dim
-        if min(self.H, self.D, self.R, self.V, self.C) <= 0:
-            raise ValueError("latent attention needs heads, head_dim, rot_dim, value_dim and latent_dim")
+        self.Q = int(spec.q_latent_dim)
+        if min(self.H, self.D, self.V, self.C) <= 0 or self.R < 0 or self.Q < 0:
+            raise ValueError("latent attention needs heads, head_dim, value_dim and latent_dim")
         if spec.window:
             raise ValueError("latent attention keeps every key")
         self.names = spec.tensor_names()
@@ -49,14 +54,19 @@ class LatentAttention(Mixer):
 
     def _n(self, role: str) -> str:
         leaf = self.names[role]
-        return f"{self.prefix}.{leaf}" + ("" if role == "latent_norm" else self.spec.weight_suffix)
+        return f"{self.prefix}.{leaf}" + ("" if role in ("latent_norm", "q_norm") else self.spec.weight_suffix)
 
     def cache_spec(self) -> Optional[KvCacheSpec]:
         return KvCacheSpec(1, self.C + self.R, None, v_head_dim=0)        # the values are the first C columns of a key row
 
     def declare(self) -> List[TensorDecl]:
         d, H, D, R, V, C = self.spec.hidden, self.H, self.D, self.R, self.V, self.C
-        out = [TensorDecl(self._n("q"), (H * (D + R), d)), TensorDecl(self._n("down"), (C + R, d)),
+        if self.Q:
+            q = [TensorDecl(self._n("q_down"), (self.Q, d)), TensorDecl(self._n("q_norm"), (self.Q,), role="norm", init="ones"),
+                 TensorDecl(self._n("q_up"), (H * (D + R), self.Q))]
+        else:
+            q = [TensorDecl(self._n("q"), (H * (D + R), d))]
+        out = q + [TensorDecl(self._n("down"), (C + R, d)),
                TensorDecl(self._n("latent_norm"), (C,), role="norm", init="ones"),
                TensorDecl(self._n("up_k"), (H * D, C)), TensorDecl(self._n("up_v"), (H * V, C)),
                TensorDecl(self._n("o"), (d, H * V))]
@@ -66,13 +76,18 @@ class LatentAttention(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         H, D, R, V, C = self.H, self.D, self.R, self.V, self.C
-        rows = [tensors[self._n("q")], tensors[self._n("down")]]
+        rows = [tensors[self._n("q_down" if self.Q else "q")], tensors[self._n("down")]]
         if self.spec.out_gate:
             rows.append(tensors[self._n("gate")])
         if len({t.dtype for t in rows}) > 1:
             rows = [t.float() for t in rows]
         self.qkv = Linear(torch.cat(rows, dim=0), None, f"{self.prefix}.q_down")
-        self.q_off, self.kv_off, self.gate_off = 0, H * (D + R), H * (D + R) + C + R
+        nq = self.Q or H * (D + R)
+        self.q_off, self.kv_off, self.gate_off = 0, nq, nq + C + R
+        self.q_norm = self.q_up = None
+        if self.Q:
+            self.q_norm = tensors[self._n("q_norm")].float().contiguous()
+            self.q_up = Linear(tensors[self._n("q_up")], None, self._n("q_up"))
         self.latent_norm = tensors[self._n("latent_norm")].float().contiguous()
         # [H, C, D]: head n's rows of Wuk, transposed, so that the product with the plain query parts is a @ w^T
         self.up_k_t = tensors[self._n("up_k")].view(H, D, C).transpose(1, 2).contiguous()
@@ -91,9 +106,15 @@ class LatentAttention(Mixer):
         q_plain = torch.empty((H, rows, D), dtype=h.dtype, device=dev)
         q_rot = torch.empty((H, rows, R), dtype=torch.float32, device=dev)
         freq = self.rope.inv_freq64(dev) if self.rope is not None else None
+        q_src = None
+        if self.Q:
+            from ..kernels import layer_ops as L
+            cq = torch.empty((T, self.Q), dtype=h.dtype, device=dev)
+            L.gated_group_norm(proj[:, :self.Q], None, self.q_norm, self.spec.norm_eps, 1, cq)
+            q_src = self.q_up.forward(cq, out_dtype=torch.float32)
         A.prepare(proj, self.q_off, self.kv_off, self.latent_norm, self.spec.norm_eps, freq, self.pairing, self.amp,
                   ctx.positions, ctx.tok_entry, table, kv.k, kv.page_size, q_plain, q_rot, T, H, D, R, C,
-                  write_cache=slot.write_cache)
+                  write_cache=slot.write_cache, q_src=q_src)
         q_lat = torch.empty((H, rows, C), dtype=torch.float32, device=dev)
         A.per_head_product(q_plain, self.up_k_t, q_lat, T)
         o_lat = torch.empty((H, rows, C), dtype=h.dtype, device=dev)

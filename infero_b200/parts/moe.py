@@ -159,3 +159,65 @@ class GroupedMoe(FeedForward):
         from ..kernels import moe as M
         M.experts(h, self.gate_up, self.down, idx, w, shared, None, y, self.act)
         return y
+
+
+class ScoredMoe(FeedForward):
+    """Ungated experts down(act(up h)) (``activation`` "relu2") chosen by scores: z = Wr h in 32-bit, s = sigmoid(z)
+    (``route_score``); the ``top`` largest scores are chosen; the weights are those scores, over their sum only with
+    ``route_renorm``.  With ``weight_input`` the weight multiplies what the expert reads, delta = sum_c expert_c(w_c h),
+    else its result.  A shared expert of the same form (``shared_intermediate``) runs for every token and is added.
+
+    The experts' matrices are stacked when the weights are bound: up [E, ff, d], down [E, d, ff]."""
+
+    def __init__(self, spec: FeedForwardSpec, prefix: str):
+        from .mlp import Relu2Mlp
+        if spec.activation != "relu2":
+            raise ValueError(f"ungated experts with activation '{spec.activation}': only 'relu2' has kernels")
+        if spec.route_score != "sigmoid":
+            raise ValueError(f"scores '{spec.route_score}' of the router's logits: only 'sigmoid' has a kernel")
+        self.spec, self.prefix = spec, prefix
+        self.E, self.top, self.ff = int(spec.experts), int(spec.top), int(spec.intermediate)
+        self.names = spec.tensor_names()
+        self.shared = None
+        if spec.shared_intermediate > 0:
+            sh = self.names["shared"]
+            sub = FeedForwardSpec(kind="relu2", hidden=spec.hidden, intermediate=spec.shared_intermediate,
+                                  names=tuple((r, f"{sh}.{self.names[r]}") for r in ("up", "down")),
+                                  weight_suffix=spec.weight_suffix)
+            self.shared = Relu2Mlp(sub, prefix)
+
+    _expert = MoeSwiGlu._expert
+    _n = MoeSwiGlu._n
+
+    def declare(self) -> List[TensorDecl]:
+        d, ff = self.spec.hidden, self.ff
+        out: List[TensorDecl] = []
+        for e in range(self.E):
+            out += [TensorDecl(self._expert(e, "up"), (ff, d)), TensorDecl(self._expert(e, "down"), (d, ff))]
+        out.append(TensorDecl(self._n("router"), (self.E, d)))
+        if self.shared is not None:
+            out += self.shared.declare()
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous()
+        self.down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous()
+        self.route = Linear(tensors[self._n("router")], None, f"{self.prefix}.route")
+        if self.shared is not None:
+            self.shared.bind(tensors)
+
+    def forward(self, ctx, h):
+        T, d = h.shape
+        z = self.route.forward(h, out_dtype=torch.float32)
+        idx, w = L.moe_select_scored(z, self.E, self.top, renorm=bool(self.spec.route_renorm))
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.forward(ctx, h)
+            if isinstance(shared, K.Partials):
+                shared = shared.materialize(torch.float32)
+            elif shared.dtype != torch.float32:
+                shared = shared.float()
+        y = torch.empty((T, d), dtype=torch.float32, device=h.device)
+        from ..kernels import moe as M
+        M.plain_experts(h, self.up, self.down, idx, w, bool(self.spec.weight_input), shared, y)
+        return y

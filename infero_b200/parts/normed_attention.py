@@ -17,9 +17,11 @@ class NormedAttention(Mixer):
     """H query heads over G key/value heads (query head h reads kv head h // (H/G)), keys ``head_dim`` wide, values
     ``value_dim`` wide.  One stacked input product gives [q | k | v | gate] (those the layer has) in 32-bit, biases
     added; ``qk_prepare`` norms and rotates q and k (``qk_norm_kind`` "projection": weighted RMS over the whole
-    projection before the rotation; "head_unit": unit RMS per head after it) and appends keys and values to the cache;
-    then attention (causal, optionally windowed, optionally with a sink in the softmax's denominator), an optional
-    sigmoid gate per head, and the output product.
+    projection before the rotation; "head_unit": unit RMS per head after it; "head": RMS per head with a weight shared
+    by the heads, before the rotation) and appends keys and values to the cache; then attention (causal, optionally
+    windowed, optionally with a sink in the softmax's denominator, optionally with a distance bias: head h's score
+    loses 2^(-b (h + 1) / H) times the distance to the key, b = ``distance_slope_exp``), an optional sigmoid gate per
+    head, and the output product.
 
     ``value_from_key``: no value projection; the cached value of a token is its key as projected.  ``borrows_cache``:
     no key or value tensors at all; the layer reads the cache of the schedule entry it is pointed at.
@@ -28,7 +30,7 @@ class NormedAttention(Mixer):
     ``input_rows`` (what to stack into a common input product), ``core`` (from product rows to the activations the
     output product takes, times a constant) and ``output_weight``."""
 
-    NORM_MODES = {"": 0, "projection": 1, "head_unit": 2}
+    NORM_MODES = {"": 0, "projection": 1, "head_unit": 2, "head": 3}
 
     def __init__(self, spec: MixerSpec, prefix: str):
         if spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
@@ -80,6 +82,8 @@ class NormedAttention(Mixer):
             out += [TensorDecl(self._n(r + "_bias", False), (n,), role="bias") for r, n in self._roles()]
         if s.qk_norm_kind == "projection":
             out += [TensorDecl(self._n(r + "_norm", False), (n,), role="norm", init="ones") for r, n in self._roles() if r != "v"]
+        if s.qk_norm_kind == "head":
+            out += [TensorDecl(self._n(r + "_norm", False), (self.D,), role="norm", init="ones") for r, _ in self._roles() if r != "v"]
         if s.out_gate:
             out.append(TensorDecl(self._n("gate"), (self.H, d)))
         out.append(TensorDecl(self._n("o"), (d, self.H * self.V)))
@@ -103,9 +107,13 @@ class NormedAttention(Mixer):
         self._out_w = tensors[self._n("o")]
         self.out = Linear(self._out_w, None, self._n("o"))
         self.q_norm = self.k_norm = None
-        if s.qk_norm_kind == "projection":
+        if s.qk_norm_kind in ("projection", "head"):
             self.q_norm = tensors[self._n("q_norm", False)].float().contiguous()
             self.k_norm = tensors[self._n("k_norm", False)].float().contiguous() if self.own_kv else None
+        self.slopes = None
+        if s.distance_slope_exp > 0:
+            self.slopes = torch.tensor([2.0 ** (-float(s.distance_slope_exp) * (h + 1) / self.H) for h in range(self.H)],
+                                       dtype=torch.float32, device=self._out_w.device)
 
     # ---- the three stages -------------------------------------------------------------------------------------------
     def input_rows(self):
@@ -140,7 +148,7 @@ class NormedAttention(Mixer):
         direct = not s.out_gate and scale == 1.0
         attn = out if direct else torch.empty((T, H * V), dtype=ctx.act_dtype, device=dev)
         from ..kernels import attention as A
-        A.paged_attention_ex(ctx, q, attn, kv, table, H, G, D, V, s.window, s.scale, s.sink)
+        A.paged_attention_ex(ctx, q, attn, kv, table, H, G, D, V, s.window, s.scale, s.sink, slopes=self.slopes)
         if not direct:
             gate = proj[:, off + self.g_off:off + self.g_off + H] if s.out_gate else None
             L.head_gate(attn, gate, out, H, V, scale)

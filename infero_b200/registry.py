@@ -95,6 +95,8 @@ def _register_builtin() -> None:
     register_architecture("Gositar", GositarConfig.from_dict, lambda c: c.to_model_spec())
     from .config.banelix import BanelixConfig
     register_architecture("Banelix", BanelixConfig.from_dict, lambda c: c.to_model_spec())
+    from .config.pibavik import PibavikConfig
+    register_architecture("Pibavik", PibavikConfig.from_dict, lambda c: c.to_model_spec())
 
 
 _register_builtin()
