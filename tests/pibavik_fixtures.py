@@ -102,10 +102,11 @@ def all_experts(cfg: dict) -> dict:
 
 
 CONFIGS["A_all"] = all_experts(A)
+CONFIGS["B_all"] = all_experts(B)
 
 
 @functools.lru_cache(maxsize=None)
-def model_dir(name: str, seed: int = 5, store: str = "bfloat16", sharp: float = 2.5) -> str:
+def model_dir(name: str, seed: int = 5, store: str = "bfloat16", sharp: float = 1.25) -> str:
     """A random model folder.  Random projections give an almost flat softmax, which hides a wrong key, so the query
     projections are multiplied by ``sharp``; and random step sizes forget within a few tokens, which hides a lost
     state, so the step's bias is moved to where a state lasts for dozens of tokens."""
@@ -117,7 +118,7 @@ def model_dir(name: str, seed: int = 5, store: str = "bfloat16", sharp: float = 
     w = load_file(p)
     for k in list(w):
         if k.endswith(".q") or k.endswith(".uq"):
-            w[k] = (w[k].float() * sharp).to(w[k].dtype)
+            w[k] = (w[k].float() * (1.0 if name == "D" else sharp)).to(w[k].dtype)     # D: wide heads are sharp enough
         if k.endswith(".dt_bias"):
             w[k] = (w[k].float() - 2.5).to(w[k].dtype)
         if k.endswith(".router"):
