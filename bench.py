@@ -287,8 +287,8 @@ def main(argv=None) -> int:
                     help="instead of the headline workload: one of the added designs (--design) beside Qwen2 at equal layer sizes, prompt and decode "
                          "steps and the kernels alone (infero_b200/tools/design_bench.py; its own JSON line)")
     ap.add_argument("--design-sizes", default="s,m")
-    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar", "banelix"],
-                    help="with --designs: which of the added designs runs beside Qwen2")
+    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar", "banelix", "pibavik"],
+                    help="with --designs: which of the added designs runs beside Qwen2 (pibavik: beside Banelix, the closest design)")
     args = ap.parse_args(argv)
 
     if args.designs and args.impl != "reference":

@@ -66,6 +66,9 @@ struct FusedQkv {
     const float* sumsq_in;
     int in_tiles;
     float inv_d, eps;
+    // A distance bias per query head (float32 [n_heads] or null): head h's score loses slopes[h] times the distance
+    // between the query and the key.  Rides here because it is one more thing the kernel needs about the queries.
+    const float* slopes;
 };
 
 // The CTA that finishes last among the splits of one (token, kv head, group tile) merges them:
@@ -252,6 +255,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int k_end = min(pos + 1, k_begin + chunk);                  // exclusive
     const int h0 = kvh * group + gt * 16;
     const int valid = min(16, group - gt * 16);
+    // the rows of the tile are heads h0 + g and h0 + g + 8: each has its own distance bias (base-2 per token)
+    const float bias0 = (fq.slopes && g < valid) ? fq.slopes[h0 + g] * 1.4426950408889634f : 0.f;
+    const float bias1 = (fq.slopes && g + 8 < valid) ? fq.slopes[h0 + g + 8] * 1.4426950408889634f : 0.f;
     float* po = partial_o + (((size_t)ti * n_heads + h0) * n_splits + split) * D;
     float* pml = partial_ml + (((size_t)ti * n_heads + h0) * n_splits + split) * 2;
     if (k_begin >= k_end) {
@@ -475,7 +481,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             __syncwarp();
         }
-        slice16<D, Layout>(qf, kt, vt, 0, kb, lo, pos, lo, pos, scale_log2, m, l, o, lane);
+        slice16<D, Layout>(qf, kt, vt, 0, kb, lo, pos, lo, pos, scale_log2, m, l, o, lane, bias0, bias1);
         __syncwarp();
     }
     if (!ok) {
@@ -708,6 +714,20 @@ int infero_attn_decode_tma_sink(const void* q, int q_stride, void* out, int out_
                       scratch, counters, n_counters, sink, stream);
 }
 
+// The same with a distance bias per head besides: slopes float32 [n_heads] (or null).
+int infero_attn_decode_tma_bias(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                                const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                                const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
+                                int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
+                                void* scratch, int* counters, int n_counters, int sink, const float* slopes,
+                                cudaStream_t stream) {
+    FusedQkv none = {};
+    none.slopes = slopes;
+    return decode_tma(q, q_stride, none, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
+                      positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
+                      scratch, counters, n_counters, sink, stream);
+}
+
 // Can the kernel below finish the q/k/v product itself?  (The vector widths its loads and stores use.)
 int infero_attn_decode_fused_supported(const float* partial, long long split_stride, int n_heads, int n_kv,
                                        int head_dim, int page_size, int rotary_dim, const void* k_cache,
@@ -737,7 +757,7 @@ int infero_attn_decode_tma_fused(const float* partial, int splits, long long spl
                                                       k_cache, v_cache),
                    "attn_decode_tma_fused: head_dim %d / rotary_dim %d / split stride %lld not supported", head_dim,
                    rotary_dim, split_stride);
-    FusedQkv fq;
+    FusedQkv fq = {};
     fq.partial = partial, fq.split_stride = split_stride, fq.bias = bias, fq.inv_freq = inv_freq;
     fq.k_cache = (bf16*)k_cache, fq.v_cache = (bf16*)v_cache, fq.splits = splits;
     fq.row_width = (n_heads + 2 * n_kv) * head_dim, fq.bias_dtype = bias_dtype, fq.rotary_dim = rotary_dim;

@@ -35,7 +35,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
                     const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
-                    int first_entry, int n_heads, int n_kv, int page_size, int window, float scale_log2, int sink) {
+                    int first_entry, int n_heads, int n_kv, int page_size, int window, float scale_log2, int sink,
+                    const float* __restrict__ slopes) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
@@ -55,6 +56,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     }
     if (e < 0) return;
     const int h = blockIdx.y, kvh = h / (n_heads / n_kv);
+    const float bias = slopes ? slopes[h] * 1.4426950408889634f : 0.f;      // the head's distance bias, base-2 per token
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int q_len = entry_q_len[e], pos0 = entry_pos0[e], tok0 = entry_q_start[e];
     const int* table = block_table + (size_t)e * max_blocks;
@@ -103,7 +105,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
             for (int sl = 0; sl < PF_KEYS / KEYS16; ++sl) {
                 const int kb = key0 + sl * KEYS16;
                 if (kb > warp_hi || kb + KEYS16 <= warp_lo) continue;
-                slice16<D>(qf, kt, kt + TILE, sl * KEYS16, kb, lo0, hi0, lo1, hi1, scale_log2, m, l, o, lane);
+                slice16<D>(qf, kt, kt + TILE, sl * KEYS16, kb, lo0, hi0, lo1, hi1, scale_log2, m, l, o, lane, bias, bias);
             }
         }
         __syncthreads();
@@ -139,7 +141,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const bf16* __restrict__ v_cache, const int* __restrict__ block_table, int max_blocks,
                    const int* __restrict__ tok_entry, const int* __restrict__ positions, int tok_first,
                    int n_heads, int n_kv, int page_size, int window, float scale_log2, int chunk,
-                   int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml) {
+                   int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                   const float* __restrict__ slopes) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
@@ -159,6 +162,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int k_end = min(pos + 1, k_begin + chunk);                  // exclusive
     const int h0 = kvh * group + gt * 16;                             // first query head of the CTA
     const int valid = min(16, group - gt * 16);
+    // the rows of the tile are heads h0 + g and h0 + g + 8: each has its own distance bias (base-2 per token)
+    const float bias0 = (slopes && g < valid) ? slopes[h0 + g] * 1.4426950408889634f : 0.f;
+    const float bias1 = (slopes && g + 8 < valid) ? slopes[h0 + g + 8] * 1.4426950408889634f : 0.f;
     float* po = partial_o + (((size_t)ti * n_heads + h0) * n_splits + split) * D;
     float* pml = partial_ml + (((size_t)ti * n_heads + h0) * n_splits + split) * 2;
     if (k_begin >= k_end) {
@@ -198,7 +204,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         __syncwarp();
         const bf16* kt = my + (size_t)(i % DEC_STAGES) * 2 * TILE;
         const int kb = k_begin + (warp + i * DEC_WARPS) * KEYS16;
-        slice16<D>(qf, kt, kt + TILE, 0, kb, lo, pos, lo, pos, scale_log2, m, l, o, lane);
+        slice16<D>(qf, kt, kt + TILE, 0, kb, lo, pos, lo, pos, scale_log2, m, l, o, lane, bias0, bias1);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -283,7 +289,7 @@ template <int D>
 int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache, const void* v_cache,
                    const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
                    const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv,
-                   int page_size, int window, float scale_log2, int sink, cudaStream_t stream) {
+                   int page_size, int window, float scale_log2, int sink, const float* slopes, cudaStream_t stream) {
     auto kern = attn_prefill_kernel<D>;
     const int smem = 2 * 2 * tile_elems<D>(PF_KEYS) * 2;
     static bool configured = false;
@@ -294,7 +300,7 @@ int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const
     dim3 grid(n_tiles, n_heads);
     launch_pdl(kern, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, entry_q_start, entry_q_len,
-               entry_pos0, n_entries, first_entry, n_heads, n_kv, page_size, window, scale_log2, sink);
+               entry_pos0, n_entries, first_entry, n_heads, n_kv, page_size, window, scale_log2, sink, slopes);
     return infero_check_launch("attn_prefill");
 }
 
@@ -302,7 +308,7 @@ template <int D>
 int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                   int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
                   int n_kv, int page_size, int window, float scale_log2, int chunk, int n_splits, float* partial_o,
-                  float* partial_ml, cudaStream_t stream) {
+                  float* partial_ml, const float* slopes, cudaStream_t stream) {
     auto kern = attn_decode_kernel<D>;
     const int tiles_bytes = DEC_WARPS * DEC_STAGES * 2 * tile_elems<D>(KEYS16) * 2;
     const int red_bytes = DEC_WARPS * 16 * (D + 2) * 4;
@@ -316,7 +322,7 @@ int launch_decode(const void* q, int q_stride, const void* k_cache, const void* 
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), n_tok);
     kern<<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache,
                                               block_table, max_blocks, tok_entry, positions, tok_first, n_heads, n_kv,
-                                              page_size, window, scale_log2, chunk, n_splits, partial_o, partial_ml);
+                                              page_size, window, scale_log2, chunk, n_splits, partial_o, partial_ml, slopes);
     return infero_check_launch("attn_decode");
 }
 
@@ -343,22 +349,33 @@ int infero_attn_mma_supported(int head_dim, int page_size) {
 // Attention for requests first_entry .. n_entries - 1 of a step (bf16), each with any number
 // of new tokens.  n_tiles = sum over those requests of ceil(q_len / 64).  q / out rows are indexed by the
 // step's token index.
-// ``sink``: the softmax's sum has one more term exp(0) that carries no value.
-int infero_attn_prefill_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+// ``sink``: the softmax's sum has one more term exp(0) that carries no value.  ``slopes`` (float32 [n_heads] or null):
+// head h's score loses slopes[h] times the distance between the query and the key.
+int infero_attn_prefill_bias(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                              const void* v_cache, const int* block_table, int max_blocks, const int* entry_q_start,
                              const int* entry_q_len, const int* entry_pos0, int n_entries, int first_entry, int n_tiles,
                              int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int sink,
-                             cudaStream_t stream) {
+                             const float* slopes, cudaStream_t stream) {
     if (n_tiles == 0) return 0;
     INFERO_REQUIRE(infero_attn_mma_supported(head_dim, page_size), "attn_prefill: head_dim %d / page_size %d not supported", head_dim, page_size);
     INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0 && n_heads <= 65535, "attn_prefill: bad head counts %d / %d", n_heads, n_kv);
     INFERO_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0, "attn_prefill: odd row strides");
     const float sl2 = scale * 1.4426950408889634f;
-#define CALL(D_) launch_prefill<D_>(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, sink, stream)
+#define CALL(D_) launch_prefill<D_>(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, sink, slopes, stream)
     DISPATCH_D(head_dim, CALL)
 #undef CALL
     infero_set_error("attn_prefill: head_dim %d has no instance", head_dim);
     return 1;
+}
+
+int infero_attn_prefill_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                             const void* v_cache, const int* block_table, int max_blocks, const int* entry_q_start,
+                             const int* entry_q_len, const int* entry_pos0, int n_entries, int first_entry, int n_tiles,
+                             int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int sink,
+                             cudaStream_t stream) {
+    return infero_attn_prefill_bias(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, entry_q_start,
+                                    entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads, n_kv, head_dim,
+                                    page_size, window, scale, sink, nullptr, stream);
 }
 
 int infero_attn_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
@@ -379,11 +396,11 @@ long long infero_attn_decode_scratch(int n_tok, int n_heads, int head_dim, int n
 // Attention for n_tok single-token requests: tokens tok_first .. tok_first + n_tok - 1 of the
 // step.  chunk (keys per split, a multiple of 16) times n_splits must cover the longest
 // visible context.  scratch: infero_attn_decode_scratch bytes.
-int infero_attn_decode_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+int infero_attn_decode_bias(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                             const void* v_cache, const int* block_table, int max_blocks, const int* tok_entry,
                             const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim,
                             int page_size, int window, float scale, int chunk, int n_splits, void* scratch, int sink,
-                            cudaStream_t stream) {
+                            const float* slopes, cudaStream_t stream) {
     if (n_tok == 0) return 0;
     INFERO_REQUIRE(infero_attn_mma_supported(head_dim, page_size), "attn_decode: head_dim %d / page_size %d not supported", head_dim, page_size);
     INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "attn_decode: bad head counts %d / %d", n_heads, n_kv);
@@ -393,7 +410,7 @@ int infero_attn_decode_sink(const void* q, int q_stride, void* out, int out_stri
     const float sl2 = scale * 1.4426950408889634f;
     float* po = (float*)scratch;
     float* pml = po + (size_t)n_tok * n_heads * n_splits * head_dim;
-#define CALL(D_) launch_decode<D_>(q, q_stride, k_cache, v_cache, block_table, max_blocks, tok_entry, positions, tok_first, n_tok, n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, stream)
+#define CALL(D_) launch_decode<D_>(q, q_stride, k_cache, v_cache, block_table, max_blocks, tok_entry, positions, tok_first, n_tok, n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, slopes, stream)
     int rc = 1;
     switch (head_dim) {
         case 16: rc = CALL(16); break;
@@ -413,6 +430,16 @@ int infero_attn_decode_sink(const void* q, int q_stride, void* out, int out_stri
     attn_combine_kernel<<<blocks, 128, 0, stream>>>(po, pml, (bf16*)out, out_stride, tok_first, n_tok, n_heads,
                                                     n_splits, head_dim, sink);
     return infero_check_launch("attn_combine");
+}
+
+int infero_attn_decode_sink(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                            const void* v_cache, const int* block_table, int max_blocks, const int* tok_entry,
+                            const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim,
+                            int page_size, int window, float scale, int chunk, int n_splits, void* scratch, int sink,
+                            cudaStream_t stream) {
+    return infero_attn_decode_bias(q, q_stride, out, out_stride, k_cache, v_cache, block_table, max_blocks, tok_entry, positions,
+                                   tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits, scratch,
+                                   sink, nullptr, stream);
 }
 
 int infero_attn_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,

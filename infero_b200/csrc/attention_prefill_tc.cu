@@ -87,7 +87,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
                        const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
                        int first_entry, int n_tiles, int n_heads, int n_kv, int heads_per_cta, int page_size, int slice,
-                       int window, float scale_log2, int sink, int* __restrict__ err_flag) {
+                       int window, float scale_log2, int sink, int* __restrict__ err_flag,
+                       const float* __restrict__ slopes) {
     using Plan = PfPlan<D>;
     constexpr int DB = Plan::DB, ST = Plan::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -294,6 +295,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int pos_r = first_pos + r;
         const int hi_r = valid ? pos_r : -1;
         const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
+        // a distance bias: the head's score loses slope * (pos_r - key).  The scores are scaled after the maximum is
+        // taken, so the bias is added to the raw score in units of 1 / scale
+        const float bias_k = slopes ? slopes[h] * 1.4426950408889634f / scale_log2 : 0.f;
         const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t head_tmem = tmem_base + (uint32_t)t * Plan::HEAD_COLS + lane_sel;
         uint64_t* my_s_full = s_full + t * 2;
@@ -316,6 +320,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int c = 0; c < KTILE / 32; ++c) tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, sv + c * 32);
             tmem_wait_ld();
+            if (bias_k != 0.f) {
+                const float first = (float)(kb - pos_r);                  // key - position of the tile's first key
+#pragma unroll
+                for (int i = 0; i < KTILE; ++i)
+                    sv[i] = __float_as_uint(fmaf(bias_k, first + (float)i, __uint_as_float(sv[i])));
+            }
             // four running maxima (and sums below): a chain of 16 dependent operations instead of 64
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (open_tile) {
@@ -424,7 +434,7 @@ template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
            const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
            const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv, int page_size,
-           int slice, int window, float scale_log2, int sink, int* err, cudaStream_t stream) {
+           int slice, int window, float scale_log2, int sink, int* err, const float* slopes, cudaStream_t stream) {
     using Plan = PfPlan<D>;
     // Two heads per CTA halve the key and value traffic, but a grid that does not fill the SMs that way
     // runs faster with one head per CTA: measured at 7B sizes 25 against 35 us at 1,024 tokens (128
@@ -449,7 +459,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     }
     launch_pdl(kern, dim3(n_kv * ((group + hpc - 1) / hpc), n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
                block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads,
-               n_kv, hpc, page_size, slice, window, scale_log2, sink, err);
+               n_kv, hpc, page_size, slice, window, scale_log2, sink, err, slopes);
     return infero_check_launch("attn_prefill_tc");
 }
 
@@ -465,13 +475,15 @@ int infero_attn_prefill_tc_supported(int head_dim, int page_size, int q_stride, 
 // n_tiles = sum over the requests first_entry .. n_entries - 1 of ceil(q_len / 128).  q is
 // [n_tokens, >= n_heads * head_dim] bf16 with row stride q_stride; the caches are
 // [num_pages, n_kv, page_size, head_dim] bf16, contiguous; all 16-byte aligned.
-// ``sink``: the softmax's sum has one more term exp(0) that carries no value.
-int infero_attn_prefill_tc_sink(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+// ``sink``: the softmax's sum has one more term exp(0) that carries no value.  ``slopes`` (float32 [n_heads] or null):
+// head h's score loses slopes[h] times the distance between the query and the key.
+int infero_attn_prefill_tc_bias(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
                                 const void* v_cache, int num_pages, const int* block_table, int max_blocks,
                                 const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
                                 int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
-                                int window, float scale, int sink, cudaStream_t stream) {
+                                int window, float scale, int sink, const float* slopes, cudaStream_t stream) {
     if (n_tiles == 0) return 0;
+    INFERO_REQUIRE(!slopes || scale > 0.f, "attn_prefill_tc: a distance bias needs a positive scale");
     INFERO_REQUIRE(infero_attn_prefill_tc_supported(head_dim, page_size, q_stride, out_stride),
                    "attn_prefill_tc: head_dim %d / page_size %d / strides %d, %d not supported", head_dim, page_size,
                    q_stride, out_stride);
@@ -492,9 +504,19 @@ int infero_attn_prefill_tc_sink(const void* q, int q_stride, int n_tokens, void*
     const float sl2 = scale * 1.4426950408889634f;
     if (head_dim == 128)
         return launch<128>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
-                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, sink, err, stream);
+                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, sink, err, slopes, stream);
     return launch<64>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
-                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, sink, err, stream);
+                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, sink, err, slopes, stream);
+}
+
+int infero_attn_prefill_tc_sink(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                                const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                                const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
+                                int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
+                                int window, float scale, int sink, cudaStream_t stream) {
+    return infero_attn_prefill_tc_bias(q, q_stride, n_tokens, out, out_stride, k_cache, v_cache, num_pages, block_table,
+                                       max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles,
+                                       n_heads, n_kv, head_dim, page_size, window, scale, sink, nullptr, stream);
 }
 
 int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,

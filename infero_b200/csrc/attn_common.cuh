@@ -109,10 +109,13 @@ __device__ __forceinline__ void load_q(uint32_t (*qf)[4], const bf16* base, size
 //   the thread's two rows (g and g + 8).
 //   Keys are DK wide and values DV wide; the key's columns start at 16-byte chunk `kchunk0` of its tile row
 //   (a tile row may hold several keys side by side).
+//   bias0 / bias1: a distance bias of the thread's two rows, in base-2 units per token: the logit of key j loses
+//   bias * (hi - j) (hi is the row's own position wherever a bias is given).
 template <int DK, int DV, typename KLayout, typename VLayout>
 __device__ __forceinline__ void slice16_kv(const uint32_t (*qf)[4], const bf16* k_tile, const bf16* v_tile, int row0,
                                            int key_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
-                                           float* m, float* l, float (*o)[4], int lane, int kchunk0 = 0) {
+                                           float* m, float* l, float (*o)[4], int lane, int kchunk0 = 0,
+                                           float bias0 = 0.f, float bias1 = 0.f) {
     const int c = lane & 3;
     float s[2][4];
 #pragma unroll
@@ -139,6 +142,10 @@ __device__ __forceinline__ void slice16_kv(const uint32_t (*qf)[4], const bf16* 
         for (int e = 0; e < 2; ++e) {
             const int j = key_base + nt * 8 + c * 2 + e;
             float a = s[nt][e] * scale_log2, b = s[nt][2 + e] * scale_log2;
+            if (bias0 != 0.f || bias1 != 0.f) {
+                a = fmaf(-bias0, (float)(hi0 - j), a);
+                b = fmaf(-bias1, (float)(hi1 - j), b);
+            }
             a = (j >= lo0 && j <= hi0) ? a : -CUDART_INF_F;
             b = (j >= lo1 && j <= hi1) ? b : -CUDART_INF_F;
             s[nt][e] = a;
@@ -197,8 +204,9 @@ __device__ __forceinline__ void slice16_kv(const uint32_t (*qf)[4], const bf16* 
 template <int D, typename Layout = PaddedRows<D>>
 __device__ __forceinline__ void slice16(const uint32_t (*qf)[4], const bf16* k_tile, const bf16* v_tile, int row0,
                                         int key_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
-                                        float* m, float* l, float (*o)[4], int lane) {
-    slice16_kv<D, D, Layout, Layout>(qf, k_tile, v_tile, row0, key_base, lo0, hi0, lo1, hi1, scale_log2, m, l, o, lane);
+                                        float* m, float* l, float (*o)[4], int lane, float bias0 = 0.f, float bias1 = 0.f) {
+    slice16_kv<D, D, Layout, Layout>(qf, k_tile, v_tile, row0, key_base, lo0, hi0, lo1, hi1, scale_log2, m, l, o, lane, 0,
+                                     bias0, bias1);
 }
 
 }  // namespace attn

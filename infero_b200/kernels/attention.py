@@ -49,26 +49,27 @@ def _arrival_counters(device) -> torch.Tensor:
 
 def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int, n_tok: int, n_heads: int,
            n_kv: int, head_dim: int, page_size: int, window: Optional[int], scale: float, chunk: int,
-           n_splits: int, sink: bool = False) -> None:
-    """``sink``: one more term exp(0) in the softmax's sum, added where the splits of a row are merged."""
+           n_splits: int, sink: bool = False, slopes=None) -> None:
+    """``sink``: one more term exp(0) in the softmax's sum, added where the splits of a row are merged.  ``slopes``
+    (float32 [H]): head h's score loses slopes[h] times the distance between the query and the key."""
     need = int(lib_scratch(n_tok, n_heads, head_dim, n_splits))
     scratch = torch.empty(need // 4, dtype=torch.float32, device=q.device)
     if lib().infero_attn_decode_tma_supported(c_int(head_dim), c_int(page_size)) and k_cache.is_contiguous() \
             and v_cache.is_contiguous():
-        _check(lib().infero_attn_decode_tma_sink(
+        _check(lib().infero_attn_decode_tma_bias(
             _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
             c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
             _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")), c_int(tok_first), c_int(n_tok),
             c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale),
             c_int(chunk), c_int(n_splits), _ptr(scratch), _ptr(_arrival_counters(q.device)), c_int(N_COUNTERS),
-            c_int(1 if sink else 0), _stream()))
+            c_int(1 if sink else 0), _ptr(slopes), _stream()))
         return
-    _check(lib().infero_attn_decode_sink(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
+    _check(lib().infero_attn_decode_bias(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
                                          _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
                                          _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),
                                          c_int(tok_first), c_int(n_tok), c_int(n_heads), c_int(n_kv), c_int(head_dim),
                                          c_int(page_size), c_int(window or 0), c_float(scale), c_int(chunk),
-                                         c_int(n_splits), _ptr(scratch), c_int(1 if sink else 0), _stream()))
+                                         c_int(n_splits), _ptr(scratch), c_int(1 if sink else 0), _ptr(slopes), _stream()))
 
 
 def decode_fused(qkv, out, k_cache, v_cache, table, tok_entry, positions, inv_freq, n_heads: int, n_kv: int,
@@ -100,13 +101,14 @@ def lib_scratch(n_tok, n_heads, head_dim, n_splits) -> int:
 
 def prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, n_entries: int,
             first_entry: int, n_tiles: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-            window: Optional[int], scale: float, sink: bool = False) -> None:
-    _check(lib().infero_attn_prefill_sink(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
+            window: Optional[int], scale: float, sink: bool = False, slopes=None) -> None:
+    _check(lib().infero_attn_prefill_bias(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
                                           _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
                                           _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
                                           _ptr(_i32(entry_pos0, "entry_pos0")), c_int(n_entries), c_int(first_entry),
                                           c_int(n_tiles), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size),
-                                          c_int(window or 0), c_float(scale), c_int(1 if sink else 0), _stream()))
+                                          c_int(window or 0), c_float(scale), c_int(1 if sink else 0), _ptr(slopes),
+                                          _stream()))
 
 
 def prefill_tc_supported(q, out, head_dim: int, page_size: int) -> bool:
@@ -117,15 +119,15 @@ def prefill_tc_supported(q, out, head_dim: int, page_size: int) -> bool:
 
 def prefill_tc(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, n_entries: int,
                first_entry: int, n_tiles: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-               window: Optional[int], scale: float, sink: bool = False) -> None:
+               window: Optional[int], scale: float, sink: bool = False, slopes=None) -> None:
     """The tcgen05 kernel: 128 query rows per block (n_tiles counts blocks of 128)."""
-    _check(lib().infero_attn_prefill_tc_sink(
+    _check(lib().infero_attn_prefill_tc_bias(
         _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(out), c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
         _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
         _ptr(_i32(entry_pos0, "entry_pos0")), c_int(n_entries), c_int(first_entry), c_int(n_tiles), c_int(n_heads),
         c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale), c_int(1 if sink else 0),
-        _stream()))
+        _ptr(slopes), _stream()))
 
 
 def shape_of_batch(q_lens: Sequence[int], pos0: Sequence[int]):
@@ -145,15 +147,15 @@ def shape_of_batch(q_lens: Sequence[int], pos0: Sequence[int]):
 def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads: int, n_kv: int, head_dim: int,
                   page_size: int, window: Optional[int], scale: float, q_lens: Sequence[int], pos0: Sequence[int],
                   entry_q_start=None, entry_q_len=None, entry_pos0=None, kv_bound: Optional[int] = None,
-                  batch_shape=None, sink: bool = False) -> None:
+                  batch_shape=None, sink: bool = False, slopes=None) -> None:
     """q: [T, >= H*D] view with rotated queries in front (row stride free); out [T, H*D].
     ``q_lens`` / ``pos0`` are the host copies of each request's new-token count and cached
     length; the device copies are made here when the caller has none.  ``kv_bound``: plan the
     decode splits for this many visible keys instead of what the batch holds now (a captured
-    step is replayed while its requests grow)."""
+    step is replayed while its requests grow).  ``slopes`` (float32 [H]): a distance bias per head."""
     if q.dtype != torch.bfloat16 or not mma_supported(head_dim, page_size):
         attention_generic(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads, n_kv, head_dim,
-                          page_size, window, scale, sink=sink)
+                          page_size, window, scale, sink=sink, slopes=slopes)
         return
     E = len(q_lens)
     if batch_shape is None:
@@ -165,7 +167,7 @@ def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads
             vis = min(vis, window + 15)
         chunk, splits = plan_decode(n_dec, n_kv, n_heads // n_kv, vis)
         decode(q, out, k_cache, v_cache, table, tok_entry, positions, 0, n_dec, n_heads, n_kv, head_dim,
-               page_size, window, scale, chunk, splits, sink=sink)
+               page_size, window, scale, chunk, splits, sink=sink, slopes=slopes)
     if n_dec < E:
         if entry_q_len is None:
             dev = q.device
@@ -178,18 +180,19 @@ def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads
         if prefill_tc_supported(q, out, head_dim, page_size) and k_cache.is_contiguous() and v_cache.is_contiguous():
             n_tiles = tiles_128
             prefill_tc(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
-                       n_heads, n_kv, head_dim, page_size, window, scale, sink=sink)
+                       n_heads, n_kv, head_dim, page_size, window, scale, sink=sink, slopes=slopes)
             return
         n_tiles = tiles_mma
         prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
-                n_heads, n_kv, head_dim, page_size, window, scale, sink=sink)
+                n_heads, n_kv, head_dim, page_size, window, scale, sink=sink, slopes=slopes)
 
 
-def paged_attention(ctx, qkv, out, kv, table, n_heads, n_kv, head_dim, window, scale, sink: bool = False) -> None:
+def paged_attention(ctx, qkv, out, kv, table, n_heads, n_kv, head_dim, window, scale, sink: bool = False, slopes=None) -> None:
     """qkv: [T, (H + 2 Hkv) D] with rotated queries in front; out [T, H*D]."""
     attention_any(qkv, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim,
                   kv.page_size, window, scale, ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len,
-                  ctx.entry_pos0, kv_bound=getattr(ctx, "kv_bound", None), batch_shape=_batch_shape(ctx), sink=sink)
+                  ctx.entry_pos0, kv_bound=getattr(ctx, "kv_bound", None), batch_shape=_batch_shape(ctx), sink=sink,
+                  slopes=slopes)
 
 
 def _batch_shape(ctx):
@@ -208,22 +211,11 @@ def paged_attention_ex(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_di
     """Attention with values of their own width and, optionally, a sink (one more term exp(0) in the softmax's sum, without
     a value) or a distance bias (``slopes`` float32 [H]: head h's score loses slopes[h] times the distance to the key).
     q [T, H*D] rotated queries; out [T, H*V].  Equal widths take the same kernels as ``paged_attention`` (the sink is a
-    term added to the sum where a row's result is divided by it); values of another width than the keys, and scores
-    with a distance bias where the tensor-core kernels have no instance for it, run on the any-type kernel."""
-    if slopes is not None:
-        if biased_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, slopes):
-            return
-        attention_generic(q, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim, kv.page_size,
-                          window, scale, value_dim=value_dim, sink=sink, slopes=slopes)
-        return
+    term added to the sum where a row's result is divided by it, the bias a term added to a score where it is masked);
+    values of another width than the keys run on the any-type kernel."""
     if value_dim == head_dim:
-        paged_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, window, scale, sink=sink)
+        paged_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, window, scale, sink=sink, slopes=slopes)
         return
     attention_generic(q, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim, kv.page_size,
-                      window, scale, value_dim=value_dim, sink=sink)
+                      window, scale, value_dim=value_dim, sink=sink, slopes=slopes)
 
-
-def biased_attention(ctx, q, out, kv, table, n_heads, n_kv, head_dim, value_dim, window, scale, slopes) -> bool:
-    """Attention with a distance bias on a tensor-core kernel; False, with nothing launched, where there is none for
-    these sizes and this element type."""
-    return False

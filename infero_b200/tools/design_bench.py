@@ -1,7 +1,7 @@
-"""Vufizen, Gositar or Banelix beside Qwen2 at equal layer sizes: whole prompt steps and decode steps, and the designs' own
-kernels one by one against their rooflines.
+"""Vufizen, Gositar or Banelix beside Qwen2, or Pibavik beside Banelix, at equal layer sizes: whole prompt steps and decode
+steps, and the designs' own kernels one by one against their rooflines.
 
-    python -m infero_b200.tools.design_bench [--design vufizen|gositar|banelix] [--sizes s,m] [--prompt 2048] [--context 2048]
+    python -m infero_b200.tools.design_bench [--design vufizen|gositar|banelix|pibavik] [--sizes s,m] [--prompt 2048] [--context 2048]
                                              [--batch 8] [--layers 8]
 
 (also ``bench.py --designs``).  Random weights made on the device, bf16.  Per size two models of the same width
@@ -17,6 +17,12 @@ group-routed expert feed-forwards alternating, four residual streams; beside Qwe
 Banelix (``--design banelix``): parallel layers (causal attention whose values are its keys beside a gated linear
 recurrence) and windowed attention layers with a sink alternating, every second attention layer reading the keys and
 values of the one before it; beside Qwen2 with the same width, head counts, heads of 128 and feed-forward.
+
+Pibavik (``--design pibavik``): of every four layers one parallel layer (gated, normed window attention beside a state-space
+recurrence), one window attention layer with a distance bias, one latent attention layer and one attention layer that reads
+the keys and values of the one two before it, all with experts chosen by sigmoid scores and a shared expert; beside Banelix,
+the closest of the other designs (parallel layers with a recurrence, window attention, borrowed caches), with the same width,
+depth, head counts, window, recurrence width and a dense feed-forward as wide as what one token uses of the experts.
 """
 from __future__ import annotations
 
@@ -73,6 +79,46 @@ BANELIX_SIZES = {
     "m": dict(width=2048, heads=16, kv=4, dim=128, window=1024, rec=2048, blocks=16, taps=4, ff=6144, vocab=32000),
     "l": dict(width=4096, heads=32, kv=8, dim=128, window=1024, rec=4096, blocks=32, taps=4, ff=11008, vocab=32000),
 }
+
+
+PIBAVIK_SIZES = {
+    "t": dict(width=256, heads=4, kv=2, dim=64, window=48, ssd_heads=8, ssd_vdim=32, state=32, groups=2, taps=4, norm_groups=2,
+              kv_rank=64, q_rank=96, experts=4, top=2, ff=128, shared=256, vocab=1000),                          # for tests
+    "s": dict(width=1024, heads=8, kv=2, dim=128, window=1024, ssd_heads=16, ssd_vdim=64, state=64, groups=2, taps=4, norm_groups=2,
+              kv_rank=256, q_rank=512, experts=16, top=2, ff=1024, shared=2048, vocab=32000),
+    "m": dict(width=2048, heads=16, kv=4, dim=128, window=1024, ssd_heads=32, ssd_vdim=64, state=128, groups=4, taps=4, norm_groups=4,
+              kv_rank=512, q_rank=768, experts=32, top=2, ff=1536, shared=3072, vocab=32000),
+    "l": dict(width=4096, heads=32, kv=8, dim=128, window=1024, ssd_heads=64, ssd_vdim=64, state=128, groups=8, taps=4, norm_groups=8,
+              kv_rank=512, q_rank=1536, experts=64, top=4, ff=2048, shared=2816, vocab=32000),
+}
+
+
+def pibavik_config(z, layers):
+    D = z["dim"]
+    left = {"heads": max(1, z["heads"] // 2), "kv_heads": max(1, z["kv"] // 2), "dim": D, "vdim": D, "scale": D ** -0.5,
+            "mask": {"size": z["window"]}, "rot": {"base": 500000.0, "dims": D // 2}}
+    right = {"heads": z["ssd_heads"], "vdim": z["ssd_vdim"], "state": z["state"], "groups": z["groups"], "conv": z["taps"],
+             "norm_groups": z["norm_groups"]}
+    par = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.7}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": z["window"]}}
+    lat = {"heads": z["heads"], "dim": D, "vdim": D, "kv_rank": z["kv_rank"], "q_rank": z["q_rank"], "scale": D ** -0.5}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared"]}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            out.append({"type": "parallel", "mixer": par, "mlp": mlp})
+        elif i % 4 == 2:
+            out.append({"type": "latent_attention", "mixer": lat, "mlp": mlp})
+        else:
+            out.append({"type": "attention", "mixer": dict(att, kv_from=i - 2) if i % 4 == 3 else att, "mlp": mlp})
+    return {"architecture": "Pibavik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": out}
+
+
+def banelix_beside_pibavik(z, layers):
+    b = dict(width=z["width"], heads=z["heads"], kv=z["kv"], dim=z["dim"], window=z["window"], rec=z["ssd_heads"] * z["ssd_vdim"],
+             blocks=z["heads"], taps=z["taps"], ff=z["top"] * z["ff"] + z["shared"], vocab=z["vocab"])
+    return banelix_config(b, layers)
 
 
 def banelix_config(z, layers):
@@ -573,9 +619,133 @@ def time_banelix_kernels(z, T, context, batch, timer, peaks):
     return rows
 
 
+def time_pibavik_kernels(z, T, context, batch, timer, peaks):
+    """Pibavik's kernels alone, each beside the kernel of another design that does the like job."""
+    import numpy as np
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.kernels import attention as A, layer_ops as L, moe as M
+    dev, bf = "cuda:0", torch.bfloat16
+    d, H, G, D, W = z["width"], z["heads"], z["kv"], z["dim"], z["window"]
+    Hn, P, N, Gs, taps, parts = z["ssd_heads"], z["ssd_vdim"], z["state"], z["groups"], z["taps"], z["norm_groups"]
+    E, top, ff = z["experts"], z["top"], z["ff"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s, dtype=bf, k=1.0: (torch.randn(s, generator=g, device=dev) * k).to(dtype)     # noqa: E731
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev)                 # noqa: E731
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    rows = {}
+
+    def note(name, ms, bytes_=0.0, flops=0.0, **more):
+        r = {"us": round(ms * 1e3, 1)}
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["hbm_frac"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["tensor_frac"] = round(flops / ms / 1e9 / tfl, 3)
+        r.update(more)
+        rows[name] = r
+
+    def batch_ctx(q_lens, pos0, ps=16):
+        E_ = len(q_lens)
+        per = [-(-(p + n) // ps) for p, n in zip(pos0, q_lens)]
+        table = torch.full((E_, max(per)), -1, dtype=torch.int32)
+        at = 0
+        for e, n in enumerate(per):
+            table[e, :n] = torch.arange(at, at + n, dtype=torch.int32)
+            at += n
+        qs = np.concatenate([[0], np.cumsum(q_lens)[:-1]])
+        ctx = types.SimpleNamespace(
+            n_entries=E_, n_tokens=int(sum(q_lens)), h_q_len=np.asarray(q_lens, dtype=np.int32), h_pos0=np.asarray(pos0, dtype=np.int32),
+            tok_entry=i32(np.repeat(np.arange(E_), q_lens)), positions=i32(np.concatenate([p + np.arange(n) for p, n in zip(pos0, q_lens)])),
+            entry_q_start=i32(qs), entry_q_len=i32(q_lens), entry_pos0=i32(pos0), entry_slot=i32(np.arange(E_)), kv_bound=None)
+        return ctx, table.to(dev), at
+
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32, device=dev)
+    for label, q_lens, pos0 in (("prefill", [T], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+        ctx, table, pages = batch_ctx(q_lens, pos0)
+        n = ctx.n_tokens
+        # ---- window attention with a distance bias beside window attention with a sink -------------------------------
+        kc, vc = rnd(pages, G, 16, D), rnd(pages, G, 16, D)
+        q, out = rnd(n, H * D), torch.empty(n, H * D, dtype=bf, device=dev)
+        w = min(W, T if label == "prefill" else context)
+        pairs = (T * w - w * w / 2) if label == "prefill" else batch * w
+        keys = T if label == "prefill" else batch * w
+        for name, sink, sl in (("window_bias_attention", False, slopes), ("window_sink_attention", True, None)):
+            ms = timer(lambda: A.attention_any(q, out, kc, vc, table, ctx.tok_entry, ctx.positions, H, G, D, 16, W, D ** -0.5,
+                                               ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0,
+                                               sink=sink, slopes=sl))
+            note(f"{name}_{label}", ms, 2.0 * G * 2 * D * keys + 4.0 * n * H * D, 2.0 * H * 2 * D * pairs)
+        # ---- from the input product to queries and the cache: the norm per head beside the norm over the projection ------
+        width = (H + 2 * G) * D
+        proj = rnd(n, width, dtype=torch.float32)
+        qo = torch.empty(n, H * D, dtype=bf, device=dev)
+        fr = torch.rand(D // 4, device=dev, dtype=torch.float64)
+        for name, mode, qw, kw in (("qk_prepare_weighted_head_norm", 3, torch.ones(D, device=dev), torch.ones(D, device=dev)),
+                                   ("qk_prepare_projection_norm", 1, torch.ones(H * D, device=dev), torch.ones(G * D, device=dev))):
+            ms = timer(lambda: L.qk_prepare(proj, 0, H * D, (H + G) * D, mode, qw, kw, 1e-5, fr, 1.0, ctx.positions, ctx.tok_entry,
+                                            table, 16, qo, kc, vc, H, G, D, D))
+            note(f"{name}_{label}", ms, n * width * (4.0 + 2.0))
+        # ---- the state-space recurrence beside the gated linear recurrence of equal width -----------------------------
+        rctx, _, _ = batch_ctx(q_lens, [0] * len(q_lens))
+        inner, CH = Hn * P, Hn * P + 2 * Gs * N
+        zx = rnd(n, 2 * inner + 2 * Gs * N + Hn, dtype=torch.float32, k=0.5)
+        cw, cb = rnd(CH, taps, dtype=torch.float32, k=0.3), rnd(CH, dtype=torch.float32, k=0.1)
+        dtb, alog, skip = rnd(Hn, dtype=torch.float32) - 3.0, rnd(Hn, dtype=torch.float32, k=0.2), rnd(Hn, dtype=torch.float32)
+        nw = torch.ones(inner, device=dev)
+        state = torch.zeros(len(q_lens), L.ssd_state_floats(Hn, N, P, Gs, taps), device=dev)
+        so = torch.empty(n, inner, dtype=bf, device=dev)
+        ms = timer(lambda: L.ssd(zx, 0, inner, inner + CH, cw, cb, dtb, alog, skip, nw, 1e-5, parts, state, rctx.tok_entry,
+                                 rctx.entry_q_start, rctx.entry_q_len, rctx.entry_slot, len(q_lens), so, Hn, Gs, N, P, 0.7,
+                                 max_q_len=max(q_lens)))
+        least = n * (zx.shape[1] * 4.0 + inner * 2.0) + 8.0 * state.numel()
+        moved = least + n * (CH * 8.0 + inner * 8.0)                       # the convolution's result and y written and read
+        note(f"ssd_{label}", ms, least, 2.0 * n * Hn * N * P * 2, gb_s_with_intermediates=round(moved / ms / 1e6, 1),
+             hbm_frac_with_intermediates=round(moved / ms / 1e6 / hbm, 3))
+        C, nb = inner, H
+        bs = C // nb
+        yx = rnd(n, 2 * C, dtype=torch.float32)
+        rw, rb_ = rnd(C, taps, dtype=torch.float32, k=0.3), rnd(C, dtype=torch.float32, k=0.1)
+        wg = rnd(nb, 2 * bs, bs, k=bs ** -0.5)
+        rb, ib, lam = rnd(C, dtype=torch.float32, k=0.1), rnd(C, dtype=torch.float32, k=0.1), rnd(C, dtype=torch.float32)
+        rstate = torch.zeros(len(q_lens), taps, C, device=dev)
+        ro = torch.empty(n, C, dtype=bf, device=dev)
+        ms = timer(lambda: L.rglru(yx, 0, C, rw, rb_, wg, rb, ib, lam, 8.0, rstate, rctx.tok_entry, rctx.entry_q_start, rctx.entry_q_len,
+                                   rctx.entry_slot, len(q_lens), ro, 0.7, max_q_len=max(q_lens), tensor_cores=True))
+        note(f"rglru_{label}", ms, n * C * (8.0 + 2.0) + 2.0 * wg.numel() + 8.0 * len(q_lens) * taps * C, 2.0 * n * 2 * C * bs)
+        # ---- ungated experts that read their weighted input beside gated experts of the same sizes --------------------
+        h = rnd(n, d)
+        up, down = rnd(E, ff, d, k=d ** -0.5), rnd(E, d, ff, k=ff ** -0.5)
+        gate_up = rnd(E, 2 * ff, d, k=d ** -0.5)
+        logits = rnd(n, E, dtype=torch.float32)
+        idx, wts = L.moe_select_scored(logits, E, top)
+        y = torch.empty(n, d, dtype=torch.float32, device=dev)
+        touched = min(E, n * top)
+        ms = timer(lambda: M.plain_experts(h, up, down, idx, wts, True, None, y))
+        note(f"experts_relu2_weighted_input_{label}", ms, touched * 2.0 * ff * d * 2 + n * d * (2.0 + 4.0), 2.0 * n * top * 2 * ff * d)
+        ms = timer(lambda: M.experts(h, gate_up, down, idx, wts, None, None, y))
+        note(f"experts_swiglu_{label}", ms, touched * 3.0 * ff * d * 2 + n * d * (2.0 + 4.0), 2.0 * n * top * 3 * ff * d)
+        ms = timer(lambda: L.moe_select_scored(logits, E, top))
+        note(f"select_by_sigmoid_scores_{label}", ms, n * E * 4.0 + n * top * 8.0)
+        ms = timer(lambda: L.moe_select(logits, E, top))
+        note(f"select_by_softmax_of_chosen_{label}", ms, n * E * 4.0 + n * top * 8.0)
+        # ---- the norm of a column slice (the queries' latent) beside add + RMSNorm ------------------------------------
+        Q = z["q_rank"]
+        wide = rnd(n, Q + z["kv_rank"], dtype=torch.float32)
+        cq = torch.empty(n, Q, dtype=bf, device=dev)
+        qn = torch.ones(Q, device=dev)
+        ms = timer(lambda: L.gated_group_norm(wide[:, :Q], None, qn, 1e-5, 1, cq))
+        note(f"latent_query_norm_{label}", ms, n * Q * (4.0 + 2.0))
+        x, yv = rnd(n, d, dtype=torch.float32), rnd(n, d, dtype=torch.float32)
+        nw2, hb = torch.ones(d, device=dev), torch.empty(n, d, dtype=bf, device=dev)
+        ms = timer(lambda: K.add_rmsnorm(x, yv, nw2, 1e-5, hb))
+        note(f"add_rmsnorm_{label}", ms, n * d * (4 + 4 + 4 + 2))
+    return rows
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="design_bench")
-    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar", "banelix"])
+    ap.add_argument("--design", default="vufizen", choices=["vufizen", "gositar", "banelix", "pibavik"])
     ap.add_argument("--sizes", default="s,m")
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--context", type=int, default=2048)
@@ -597,14 +767,16 @@ def main(argv=None) -> int:
     timer = _Timer()
     sizes, design_cfg, beside_cfg, each = {"vufizen": (SIZES, vufizen_config, qwen2_config, time_kernels),
                                            "gositar": (GOSITAR_SIZES, gositar_config, qwen2_beside_gositar, time_gositar_kernels),
-                                           "banelix": (BANELIX_SIZES, banelix_config, qwen2_beside_banelix, time_banelix_kernels)}[args.design]
+                                           "banelix": (BANELIX_SIZES, banelix_config, qwen2_beside_banelix, time_banelix_kernels),
+                                           "pibavik": (PIBAVIK_SIZES, pibavik_config, banelix_beside_pibavik, time_pibavik_kernels)}[args.design]
+    beside = "banelix" if args.design == "pibavik" else "qwen2"
     out = {"bench": "designs", "design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.prompt, "context": args.context,
            "batch": args.batch, "layers": args.layers, "peaks": peaks, "sizes": {}}
     for name in [s for s in args.sizes.split(",") if s]:
         z = sizes[name]
         out["sizes"][name] = {"shape": z,
                               args.design: time_model(design_cfg(z, args.layers), args.prompt, args.context, args.batch, timer),
-                              "qwen2": time_model(beside_cfg(z, args.layers), args.prompt, args.context, args.batch, timer)}
+                              beside: time_model(beside_cfg(z, args.layers), args.prompt, args.context, args.batch, timer)}
         print(f"[design_bench] {name}: {json.dumps(out['sizes'][name])}", file=sys.stderr, flush=True)
     if args.kernels_at:
         out["kernels"] = {"size": args.kernels_at,

@@ -74,3 +74,19 @@ def test_design_bench_of_gositar(capsys):
     assert {"latent_attention_prefill", "latent_attention_decode", "moe_experts_clamped_decode", "hyper_step_prefill",
             "per_head_up_k_prefill", "dense_relu2_decode"} <= set(rows)
     assert all(r["us"] > 0 for r in rows.values())
+
+
+def test_design_bench_of_pibavik(capsys):
+    """``bench.py --designs --design pibavik`` at a size made for tests: beside Banelix, the closest design."""
+    import json
+    from infero_b200.tools import design_bench
+    assert design_bench.main(["--design", "pibavik", "--sizes", "t", "--prompt", "600", "--context", "300", "--batch", "3",
+                              "--layers", "4", "--kernels-at", "t"]) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["design"] == "pibavik" and set(line["sizes"]["t"]) == {"shape", "pibavik", "banelix"}
+    for design in ("pibavik", "banelix"):
+        assert line["sizes"]["t"][design]["prefill_tok_s"] > 0 and line["sizes"]["t"][design]["decode_tok_s"] > 0
+    rows = line["kernels"]["rows"]
+    assert {"window_bias_attention_prefill", "window_bias_attention_decode", "ssd_prefill", "ssd_decode", "rglru_decode",
+            "experts_relu2_weighted_input_prefill", "experts_swiglu_decode", "latent_query_norm_prefill"} <= set(rows)
+    assert all(r["us"] > 0 for r in rows.values())
