@@ -18,22 +18,32 @@
 // conv:  one thread per (token, channel); inputs before the step's first token come from the slot's tail.
 // tail:  after conv, one thread per (request, channel) moves the tail on by the request's new tokens.
 // scan:  a block per (request, head, block of P columns); a thread keeps 16 rows of one column of S in registers;
-//        tokens are staged eight at a time in shared memory; the products with C are added up over the row groups in
+//        tokens are staged sixteen at a time in shared memory by asynchronous copies, the next sixteen arriving while
+//        these are worked on; the products with C are added up over the row groups in
 //        a fixed order.  The tokens of a request run in order, so the arithmetic of a token does not depend on how the
-//        prompt was cut or on the rest of the batch.  A long portion is cut into chunks of the request's own tokens
-//        that run side by side: pass 1 (every chunk from S = 0: its end state and the product of its decays), a
+//        prompt was cut or on the rest of the batch beyond rounding.  Where requests, heads and column blocks do not
+//        fill the device, a long portion is cut into chunks of the request's own tokens that run side by side: pass 1 (every chunk from S = 0: its end state and the product of its decays), a
 //        chain over the chunks (start states), pass 2 (the outputs from the start states).
 // gated group norm: one block per (token, part).
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace {
 
 constexpr int NPT = 16;            // rows of S a thread keeps
-constexpr int TCH = 8;             // tokens staged at a time
+constexpr int TCH = 16;            // tokens staged at a time (two stages: the next one arrives while this one is worked on)
 constexpr int MAX_TAPS = 16;
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ void copy4_async(float* dst_smem, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy16_async(float* dst_smem, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copies_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 __global__ void ssd_conv_kernel(const float* __restrict__ proj, int proj_stride, int x_off, const float* __restrict__ conv_w,
                                 const float* __restrict__ conv_b, int taps, const float* __restrict__ state,
@@ -83,21 +93,25 @@ __global__ void ssd_tail_kernel(const float* __restrict__ proj, int proj_stride,
 // mode 0: from the slot's state over all the request's tokens, outputs written, the slot's state updated.
 // mode 1: chunk k of the request from S = 0, no outputs; end state and product of decays to chunk_state / chunk_decay.
 // mode 2: chunk k from chunk_state[k], outputs written; the last chunk updates the slot.
+// FULL: the state's rows are a multiple of 16, so a thread's 16 rows always exist and its B and C values are four aligned
+// 16-byte loads; the arithmetic (and its order) is the same either way.
+template <int MODE, bool FULL>
 __global__ void ssd_scan_kernel(const float* __restrict__ u, int CH, const float* __restrict__ proj, int proj_stride,
                                 int dt_off, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ skip, float* __restrict__ state, long long state_stride,
                                 long long s_off, const int* __restrict__ entry_q_start, const int* __restrict__ entry_q_len,
                                 const int* __restrict__ entry_slot, float* __restrict__ y, int heads, int groups, int N,
-                                int P, int PT, int mode, int chunk_len, int max_chunks, float* __restrict__ chunk_state,
+                                int P, int PT, int chunk_len, int max_chunks, float* __restrict__ chunk_state,
                                 float* __restrict__ chunk_decay) {
     extern __shared__ float sm[];
+    constexpr int mode = MODE;
     const int NJ = (N + NPT - 1) / NPT;
-    float* xs = sm;                                  // [TCH][PT]
-    float* Bs = xs + TCH * PT;                       // [TCH][N]
-    float* Cs = Bs + TCH * N;                        // [TCH][N]
-    float* dts = Cs + TCH * N;                       // [TCH]
-    float* dec = dts + TCH;                          // [TCH]
-    float* yp = dec + TCH;                           // [TCH][NJ][PT]
+    float* xs = sm;                                  // [2][TCH][PT]
+    float* Bs = xs + 2 * TCH * PT;                   // [2][TCH][N]
+    float* Cs = Bs + 2 * TCH * N;                    // [2][TCH][N]
+    float* dts = Cs + 2 * TCH * N;                   // [2][TCH]
+    float* dec = dts + 2 * TCH;                      // [2][TCH]
+    float* yp = dec + 2 * TCH;                       // [TCH][NJ][PT]
     const int e = blockIdx.x, h = blockIdx.y;
     const int pb = blockIdx.z % ((P + PT - 1) / PT), k = blockIdx.z / ((P + PT - 1) / PT);
     const int n_new = entry_q_len[e];
@@ -137,36 +151,82 @@ __global__ void ssd_scan_kernel(const float* __restrict__ u, int CH, const float
     }
     float total_decay = 1.f;
 
-    for (int c0 = t0; c0 < t1; c0 += TCH) {
+    // a stage: TCH tokens' x (this block's columns), B, C, step size and decay; filled by asynchronous copies
+    // (no division in here: thread row j takes tokens j, j + rows, ...; warp w the B and C rows of tokens w, w + warps, ...)
+    const int trows = nthr / PT, warp = tid >> 5, lane = tid & 31, nwarps = nthr >> 5;
+    const bool wide = FULL && (inner & 3) == 0;      // rows of B and C start on 16-byte boundaries
+    auto fill = [&](int c0, int buf) {
         const int nt = min(TCH, t1 - c0);
-        __syncthreads();                             // the chunk before has been read
-        for (int i = tid; i < nt * PT; i += nthr) {
-            const int tt = i / PT, pp = pb * PT + i % PT;
-            xs[i] = pp < P ? u[(size_t)(first + c0 + tt) * CH + (size_t)h * P + pp] : 0.f;
+        float* xb = xs + buf * TCH * PT;
+        float* Bb = Bs + buf * TCH * N;
+        float* Cb = Cs + buf * TCH * N;
+        if (j < trows) {
+            for (int tt = j; tt < nt; tt += trows) {
+                if (p < P) copy4_async(xb + tt * PT + pl, u + (size_t)(first + c0 + tt) * CH + (size_t)h * P + p);
+                else xb[tt * PT + pl] = 0.f;
+            }
         }
-        for (int i = tid; i < nt * N; i += nthr) {
-            const int tt = i / N, n = i % N;
+        for (int tt = warp; tt < nt; tt += nwarps) {
             const float* row = u + (size_t)(first + c0 + tt) * CH + inner + (size_t)g * N;
-            Bs[tt * N + n] = row[n];
-            Cs[tt * N + n] = row[(size_t)groups * N + n];
+            if (wide) {
+                for (int n = lane * 4; n < N; n += 128) {
+                    copy16_async(Bb + tt * N + n, row + n);
+                    copy16_async(Cb + tt * N + n, row + (size_t)groups * N + n);
+                }
+            } else {
+                for (int n = lane; n < N; n += 32) {
+                    copy4_async(Bb + tt * N + n, row + n);
+                    copy4_async(Cb + tt * N + n, row + (size_t)groups * N + n);
+                }
+            }
         }
         if (tid < nt) {
             const float d = softplus_f(proj[(size_t)(first + c0 + tid) * proj_stride + dt_off + h] + bias);
-            dts[tid] = d;
-            dec[tid] = expf(-rate * d);
+            dts[buf * TCH + tid] = d;
+            dec[buf * TCH + tid] = expf(-rate * d);
         }
-        __syncthreads();
+    };
+    fill(t0, 0);
+    copies_commit();
+    int buf = 0;
+    for (int c0 = t0; c0 < t1; c0 += TCH, buf ^= 1) {
+        const int nt = min(TCH, t1 - c0);
+        if (c0 + TCH < t1) fill(c0 + TCH, buf ^ 1);  // (the other stage was let go of at the end of the round before)
+        copies_commit();
+        copies_wait_all_but_one();
+        __syncthreads();                             // this stage has landed, for every thread
+        const float* xb = xs + buf * TCH * PT;
         for (int tt = 0; tt < nt; ++tt) {
-            const float a = dec[tt], dx = dts[tt] * xs[tt * PT + pl];
-            const float* Bt = Bs + tt * N + j * NPT;
-            const float* Ct = Cs + tt * N + j * NPT;
+            const float a = dec[buf * TCH + tt], dx = dts[buf * TCH + tt] * xb[tt * PT + pl];
+            const float* Bt = Bs + (buf * TCH + tt) * N + j * NPT;
+            const float* Ct = Cs + (buf * TCH + tt) * N + j * NPT;
             float acc = 0.f;
             if (j < NJ) {
+                if (FULL) {
+                    const float4* B4 = reinterpret_cast<const float4*>(Bt);
+                    const float4* C4 = reinterpret_cast<const float4*>(Ct);
 #pragma unroll
-                for (int r = 0; r < NPT; ++r) {
-                    if (j * NPT + r < N) {
-                        S[r] = fmaf(a, S[r], Bt[r] * dx);
-                        acc = fmaf(S[r], Ct[r], acc);
+                    for (int q = 0; q < NPT / 4; ++q) {
+                        const float4 b = B4[q];
+                        S[4 * q] = fmaf(a, S[4 * q], b.x * dx);
+                        S[4 * q + 1] = fmaf(a, S[4 * q + 1], b.y * dx);
+                        S[4 * q + 2] = fmaf(a, S[4 * q + 2], b.z * dx);
+                        S[4 * q + 3] = fmaf(a, S[4 * q + 3], b.w * dx);
+                        if (mode != 1) {
+                            const float4 c = C4[q];
+                            acc = fmaf(S[4 * q], c.x, acc);
+                            acc = fmaf(S[4 * q + 1], c.y, acc);
+                            acc = fmaf(S[4 * q + 2], c.z, acc);
+                            acc = fmaf(S[4 * q + 3], c.w, acc);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < NPT; ++r) {
+                        if (j * NPT + r < N) {
+                            S[r] = fmaf(a, S[r], Bt[r] * dx);
+                            if (mode != 1) acc = fmaf(S[r], Ct[r], acc);
+                        }
                     }
                 }
                 if (mode != 1) yp[(tt * NJ + j) * PT + pl] = acc;
@@ -175,14 +235,15 @@ __global__ void ssd_scan_kernel(const float* __restrict__ u, int CH, const float
         }
         if (mode != 1) {
             __syncthreads();
-            for (int i = tid; i < nt * PT; i += nthr) {
-                const int tt = i / PT, pp = i % PT;
-                if (pb * PT + pp >= P) continue;
-                float acc = 0.f;
-                for (int jj = 0; jj < NJ; ++jj) acc += yp[(tt * NJ + jj) * PT + pp];
-                y[(size_t)(first + c0 + tt) * inner + (size_t)h * P + pb * PT + pp] = fmaf(dskip, xs[tt * PT + pp], acc);
+            if (j < trows && p < P) {
+                for (int tt = j; tt < nt; tt += trows) {
+                    float acc = 0.f;
+                    for (int jj = 0; jj < NJ; ++jj) acc += yp[(tt * NJ + jj) * PT + pl];
+                    y[(size_t)(first + c0 + tt) * inner + (size_t)h * P + p] = fmaf(dskip, xb[tt * PT + pl], acc);
+                }
             }
         }
+        __syncthreads();                             // this stage and the partial products may be overwritten
     }
     if (!live) return;
     if (mode == 1) {
@@ -210,11 +271,25 @@ __global__ void ssd_chain_kernel(const float* __restrict__ state, long long stat
     const int n_new = entry_q_len[e];
     const int n_chunks = n_new >= 2 * chunk_len ? (n_new + chunk_len - 1) / chunk_len : (n_new > 0 ? 1 : 0);
     float cur = state[(long long)entry_slot[e] * state_stride + s_off + i];
-    for (int k = 0; k + 1 < n_chunks; ++k) {
-        float* slot = chunk_state + ((long long)e * max_chunks + k) * heads * per_head + i;
-        const float end = *slot;
-        *slot = cur;                                 // chunk k starts from here
-        cur = fmaf(chunk_decay[((long long)e * max_chunks + k) * heads + h], cur, end);
+    constexpr int AHEAD = 8;                         // end states and decays of eight chunks are fetched together
+    for (int k0 = 0; k0 + 1 < n_chunks; k0 += AHEAD) {
+        float end[AHEAD], dec[AHEAD];
+#pragma unroll
+        for (int a = 0; a < AHEAD; ++a) {
+            const int k = k0 + a;
+            if (k + 1 < n_chunks) {
+                end[a] = chunk_state[((long long)e * max_chunks + k) * heads * per_head + i];
+                dec[a] = chunk_decay[((long long)e * max_chunks + k) * heads + h];
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < AHEAD; ++a) {
+            const int k = k0 + a;
+            if (k + 1 < n_chunks) {
+                chunk_state[((long long)e * max_chunks + k) * heads * per_head + i] = cur;      // chunk k starts from here
+                cur = fmaf(dec[a], cur, end[a]);
+            }
+        }
     }
     if (n_chunks > 0) chunk_state[((long long)e * max_chunks + n_chunks - 1) * heads * per_head + i] = cur;
 }
@@ -292,37 +367,56 @@ int infero_ssd_scan(const float* u, const float* proj, int proj_stride, int dt_o
     const long long s_off = (long long)(taps - 1) * CH;
     const int NJ = (N + NPT - 1) / NPT;
     const int L = infero_ssd_chunk_len();
-    const bool chunked = scratch != nullptr && max_q_len >= 2 * L;
-    const int max_chunks = chunked ? (max_q_len + L - 1) / L : 1;
-    // columns of S per block: all of them up to 64, fewer while the grid leaves multiprocessors idle
-    int PT = P < 64 ? P : 64;
     const int sms = sm_count > 0 ? sm_count : 148;
-    while (PT > 8 && PT % 2 == 0 && (long long)n_entries * heads * max_chunks * ((P + PT - 1) / PT) < sms) PT /= 2;
-    while (PT * NJ > 1024) PT = (PT + 1) / 2;
+    // Columns of S per block: all of them up to 64, fewer (down to 8) while the grid would leave multiprocessors idle.
+    // Blocks over the columns cost nothing extra, chunks cost a second pass: a step is cut into chunks only when
+    // requests, heads and column blocks together do not fill the device.
+    auto pick = [&](int chunks) {
+        int pt = P < 64 ? P : 64;
+        while (pt > 8 && pt % 2 == 0 && (long long)n_entries * heads * chunks * ((P + pt - 1) / pt) < 2ll * sms) pt /= 2;
+        return pt;
+    };
+    int PT = pick(1);
+    static const int chunk_rule = [] { const char* e = getenv("INFERO_SSD_CHUNKS"); return e ? atoi(e) : 1; }();
+    // INFERO_SSD_CHUNKS: 1 (default) long portions always run by chunks; 2 only where the grid would not fill the device; 0 never
+    const bool chunked = scratch != nullptr && max_q_len >= 2 * L && chunk_rule != 0 &&
+                         (chunk_rule == 1 || (long long)n_entries * heads * ((P + PT - 1) / PT) < sms);
+    const int max_chunks = chunked ? (max_q_len + L - 1) / L : 1;
+    if (chunked) PT = pick(max_chunks);
+    static const int max_threads = [] { const char* e = getenv("INFERO_SSD_THREADS"); return e ? atoi(e) : 256; }();
+    while (PT * NJ > max_threads && PT > 1) PT = (PT + 1) / 2;          // (the registers of 512 threads of the widest instance fit one multiprocessor)
     const int pbs = (P + PT - 1) / PT;
     const int threads = ((PT * NJ + 31) / 32) * 32;
-    const size_t smem = (size_t)TCH * (PT + 2 * N + 2 + NJ * PT) * sizeof(float);
+    const size_t smem = (size_t)TCH * (2 * (PT + 2 * N + 2) + NJ * PT) * sizeof(float);
     INFERO_REQUIRE(smem <= 200 * 1024, "ssd: state %d x %d needs %zu bytes of shared memory", N, P, smem);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(ssd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool full = N % NPT == 0;
+    auto k0 = full ? ssd_scan_kernel<0, true> : ssd_scan_kernel<0, false>;
+    auto k1 = full ? ssd_scan_kernel<1, true> : ssd_scan_kernel<1, false>;
+    auto k2 = full ? ssd_scan_kernel<2, true> : ssd_scan_kernel<2, false>;
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     float* chunk_state = scratch;
     float* chunk_decay = scratch ? scratch + (long long)n_entries * max_chunks * heads * N * P : nullptr;
     if (!chunked) {
-        ssd_scan_kernel<<<dim3(n_entries, heads, pbs), threads, smem, stream>>>(
+        k0<<<dim3(n_entries, heads, pbs), threads, smem, stream>>>(
             u, CH, proj, proj_stride, dt_off, dt_bias, a_log, skip, state, state_stride, s_off, entry_q_start, entry_q_len,
-            entry_slot, y, heads, groups, N, P, PT, 0, 0, 1, nullptr, nullptr);
+            entry_slot, y, heads, groups, N, P, PT, 0, 1, nullptr, nullptr);
         return infero_check_launch("ssd_scan");
     }
     INFERO_REQUIRE((long long)pbs * max_chunks <= 65535, "ssd: a portion of %d tokens is too long for one launch", max_q_len);
     const dim3 grid(n_entries, heads, pbs * max_chunks);
-    ssd_scan_kernel<<<grid, threads, smem, stream>>>(u, CH, proj, proj_stride, dt_off, dt_bias, a_log, skip, state, state_stride,
-                                                    s_off, entry_q_start, entry_q_len, entry_slot, y, heads, groups, N, P, PT, 1,
-                                                    L, max_chunks, chunk_state, chunk_decay);
+    k1<<<grid, threads, smem, stream>>>(u, CH, proj, proj_stride, dt_off, dt_bias, a_log, skip, state, state_stride,
+                                                       s_off, entry_q_start, entry_q_len, entry_slot, y, heads, groups, N, P, PT,
+                                                       L, max_chunks, chunk_state, chunk_decay);
     const long long per_head = (long long)N * P;
     ssd_chain_kernel<<<dim3((unsigned)((heads * per_head + 255) / 256), n_entries), 256, 0, stream>>>(
         state, state_stride, s_off, entry_q_len, entry_slot, chunk_state, chunk_decay, heads, per_head, L, max_chunks);
-    ssd_scan_kernel<<<grid, threads, smem, stream>>>(u, CH, proj, proj_stride, dt_off, dt_bias, a_log, skip, state, state_stride,
-                                                    s_off, entry_q_start, entry_q_len, entry_slot, y, heads, groups, N, P, PT, 2,
-                                                    L, max_chunks, chunk_state, chunk_decay);
+    k2<<<grid, threads, smem, stream>>>(u, CH, proj, proj_stride, dt_off, dt_bias, a_log, skip, state, state_stride,
+                                                       s_off, entry_q_start, entry_q_len, entry_slot, y, heads, groups, N, P, PT,
+                                                       L, max_chunks, chunk_state, chunk_decay);
     return infero_check_launch("ssd_scan_chunked");
 }
 
