@@ -19,11 +19,11 @@
 // tail:  after conv, one thread per (request, channel) moves the tail on by the request's new tokens.
 // scan:  a block per (request, head, block of P columns); a thread keeps 16 rows of one column of S in registers;
 //        tokens are staged sixteen at a time in shared memory by asynchronous copies, the next sixteen arriving while
-//        these are worked on; the products with C are added up over the row groups in
-//        a fixed order.  The tokens of a request run in order, so the arithmetic of a token does not depend on how the
-//        prompt was cut or on the rest of the batch beyond rounding.  Where requests, heads and column blocks do not
-//        fill the device, a long portion is cut into chunks of the request's own tokens that run side by side: pass 1 (every chunk from S = 0: its end state and the product of its decays), a
-//        chain over the chunks (start states), pass 2 (the outputs from the start states).
+//        these are worked on; the products with C are added up over the row groups in a fixed order.  The tokens of a
+//        request run in order, so the arithmetic of a token does not depend on how the prompt was cut or on the rest
+//        of the batch beyond rounding.  A portion of 256 tokens and more is cut into chunks of 128 of the request's
+//        own tokens that run side by side: pass 1 (every chunk from S = 0: its end state and the product of its
+//        decays), a chain over the chunks (start states), pass 2 (the outputs from the start states).
 // gated group norm: one block per (token, part).
 #include "common.cuh"
 #include <stdlib.h>
@@ -384,7 +384,8 @@ int infero_ssd_scan(const float* u, const float* proj, int proj_stride, int dt_o
     const int max_chunks = chunked ? (max_q_len + L - 1) / L : 1;
     if (chunked) PT = pick(max_chunks);
     static const int max_threads = [] { const char* e = getenv("INFERO_SSD_THREADS"); return e ? atoi(e) : 256; }();
-    while (PT * NJ > max_threads && PT > 1) PT = (PT + 1) / 2;          // (the registers of 512 threads of the widest instance fit one multiprocessor)
+    // (256 threads a block measured best: three blocks' registers fit a multiprocessor; INFERO_SSD_THREADS changes it)
+    while (PT * NJ > max_threads && PT > 1) PT = (PT + 1) / 2;
     const int pbs = (P + PT - 1) / PT;
     const int threads = ((PT * NJ + 31) / 32) * 32;
     const size_t smem = (size_t)TCH * (2 * (PT + 2 * N + 2) + NJ * PT) * sizeof(float);
