@@ -191,7 +191,7 @@ __global__ void ssd_scan_kernel(const float* __restrict__ u, int CH, const float
     int buf = 0;
     for (int c0 = t0; c0 < t1; c0 += TCH, buf ^= 1) {
         const int nt = min(TCH, t1 - c0);
-        if (c0 + TCH < t1) fill(c0 + TCH, buf ^ 1);  // (the other stage was let go of at the end of the round before)
+        if (c0 + TCH < t1) fill(c0 + TCH, buf ^ 1);  // (the other stage was let go of at the end of the pass before)
         copies_commit();
         copies_wait_all_but_one();
         __syncthreads();                             // this stage has landed, for every thread
