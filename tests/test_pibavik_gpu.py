@@ -319,6 +319,37 @@ def test_the_gated_normed_turned_window_attention(dtype, H, G, D, V, window, dim
     assert _rel(got[:, :H * V], want) < (2e-5 if dtype == "float32" else 3e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("back", [0, 1, 16, 38, 39, 40, 41, 48])
+@pytest.mark.parametrize("decode", [False, True])
+def test_the_gated_mixers_window_keeps_a_key_that_stands_out_and_drops_it_one_token_later(dtype, back, decode):
+    """The left mixer's own window of 40, with normed heads: the query of the last token is an earlier token's key."""
+    H, G, D, V, window, d = 2, 1, 64, 64, 40, 128
+    m = _left_dict(H, G, D, V, window, 0, scale=0.25)
+    a = _Alone(_left_spec(H, G, D, V, window, d, 0, scale=0.25), dtype, seed=back)
+    a.w["l0.mix.q"] = torch.cat([a.w["l0.mix.k"]] * H)
+    a.w["l0.mix.q"][:, d // 2:] *= -1
+    a.w["l0.mix.q.norm"] = a.w["l0.mix.k.norm"].clone()
+    _rebind(a)
+    g = torch.Generator().manual_seed(back)
+    n = 70
+    h = torch.randn(n, d, generator=g)
+    h[n - 1] = h[n - 1 - back]
+    h[n - 1, d // 2:] *= -1
+    if dtype == "bfloat16":
+        h = h.bfloat16().float()
+    want = PP.left_attention(h.double(), a.weights(), "mix", m, 1e-5)[:, :H * V]
+    if decode:
+        got = torch.cat([a.step([("r", h[:n - 50])])["r"]] + [a.step([("r", h[p:p + 1])])["r"] for p in range(n - 50, n)])
+    else:
+        got = torch.cat([a.step([("r", h[:11])])["r"], a.step([("r", h[11:])])["r"]])
+    assert _rel(got[:, :H * V], want) < (3e-5 if dtype == "float32" else 4e-2)
+    h2 = h.clone()
+    h2[n - 1 - back] = 0.0
+    moved = _rel(PP.left_attention(h2.double(), a.weights(), "mix", m, 1e-5)[-1:, :H * V], want[-1:])
+    assert (moved > 0.3) if back < window else (moved < 1e-9)
+
+
 def _ssd_spec(Hn, P, N, G, taps, parts, d, names=()):
     from infero_b200.config.spec import MixerSpec
     return MixerSpec(kind="ssd", hidden=d, num_heads=Hn, value_dim=P, state_dim=N, rec_groups=G, norm_groups=parts,
