@@ -94,14 +94,18 @@ moe_select_kernel(const float* __restrict__ logits, int stride, int gate_col, in
 // Scores are sigmoid(logit); the `top` largest are chosen by score (ties: the lower index); weights are the scores,
 // divided by the sum of the chosen ones where `renorm`.  One warp per token.
 __global__ void __launch_bounds__(RWARPS * 32)
-moe_select_scored_kernel(const float* __restrict__ logits, int stride, int* __restrict__ top_idx,
-                         float* __restrict__ top_w, int n_tokens, int E, int top, int renorm) {
+moe_select_scored_kernel(const float* __restrict__ logits, int stride, int splits, long long split_stride,
+                         int* __restrict__ top_idx, float* __restrict__ top_w, int n_tokens, int E, int top, int renorm) {
     __shared__ float sc[RWARPS][MAX_E];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * RWARPS + warp;
     if (t >= n_tokens) return;
     const float* zr = logits + (size_t)t * stride;
-    for (int e = lane; e < E; e += 32) sc[warp][e] = 1.0f / (1.0f + expf(-zr[e]));
+    for (int e = lane; e < E; e += 32) {
+        float z = zr[e];                              // the logits may come as split-K partial sums, added up in order
+        for (int sp = 1; sp < splits; ++sp) z += zr[(size_t)sp * split_stride + e];
+        sc[warp][e] = 1.0f / (1.0f + expf(-z));
+    }
     __syncwarp();
     float mine = 0.f, sum = 0.f;
     int mine_e = 0;
@@ -254,7 +258,7 @@ template <typename T>
 __global__ void __launch_bounds__(EWARPS * 32)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ top_idx,
                 const float* __restrict__ top_w, const float* __restrict__ shared, const float* __restrict__ shared_gate,
-                float* __restrict__ y, int d, int ff, int top) {
+                float* __restrict__ y, int d, int ff, int top, int shared_splits = 1, long long shared_stride = 0) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.y;
     const int i = blockIdx.x * EWARPS + warp;
@@ -266,7 +270,11 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int
         acc = top_w ? fmaf(top_w[(size_t)t * top + c], v, acc) : acc + v;
     }
     if (lane == 0) {
-        if (shared) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared[(size_t)t * d + i], acc);
+        if (shared) {
+            float sh = shared[(size_t)t * d + i];                 // (split-K partial sums of the shared expert: added up in order)
+            for (int sp = 1; sp < shared_splits; ++sp) sh += shared[(size_t)sp * shared_stride + (size_t)t * d + i];
+            acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, sh, acc);
+        }
         y[(size_t)t * d + i] = acc;
     }
 }
@@ -297,21 +305,25 @@ int infero_moe_select_grouped(const float* logits, int stride, const float* corr
     return infero_check_launch("moe_select_grouped");
 }
 
-int infero_moe_select_scored(const float* logits, int stride, int* top_idx, float* top_w, int n_tokens, int E, int top,
-                             int renorm, cudaStream_t stream) {
+// logits: float32 [splits][tokens, stride] (split_stride elements apart); the value is the sum over the splits.
+int infero_moe_select_scored(const float* logits, int stride, int splits, long long split_stride, int* top_idx, float* top_w,
+                             int n_tokens, int E, int top, int renorm, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(E >= 1 && E <= MAX_E && top >= 1 && top <= E && top <= MAX_TOP,
                    "moe select: %d experts (at most %d), top %d (at most %d)", E, MAX_E, top, MAX_TOP);
-    moe_select_scored_kernel<<<(n_tokens + RWARPS - 1) / RWARPS, RWARPS * 32, 0, stream>>>(logits, stride, top_idx, top_w,
-                                                                                         n_tokens, E, top, renorm);
+    INFERO_REQUIRE(splits >= 1, "moe select: %d splits", splits);
+    moe_select_scored_kernel<<<(n_tokens + RWARPS - 1) / RWARPS, RWARPS * 32, 0, stream>>>(logits, stride, splits, split_stride,
+                                                                                         top_idx, top_w, n_tokens, E, top, renorm);
     return infero_check_launch("moe_select_scored");
 }
 
 // Ungated experts with the squared relu: up [E, ff, d], down [E, d, ff].  weight_input: the pair's weight multiplies what
 // the expert reads and the choices are added up as they are; else it multiplies the expert's result.
+// shared: float32 [shared_splits][tokens, d] (shared_stride elements apart; the value is the sum over the splits) or null.
 int infero_moe_experts_plain_streamed(const void* h, int h_stride, const void* up, const void* down, int dtype,
                                       const int* top_idx, const float* top_w, int weight_input, const float* shared,
-                                      void* act, float* y, int n_tokens, int d, int ff, int top, cudaStream_t stream) {
+                                      int shared_splits, long long shared_stride, void* act, float* y, int n_tokens, int d,
+                                      int ff, int top, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(n_tokens * (long long)top <= 65535 && n_tokens <= 65535, "moe: %d tokens are too many for the streaming path", n_tokens);
     const dim3 gu((ff + EWARPS - 1) / EWARPS, n_tokens * top), gd((d + EWARPS - 1) / EWARPS, n_tokens);
@@ -321,12 +333,12 @@ int infero_moe_experts_plain_streamed(const void* h, int h_stride, const void* u
         moe_up_plain_kernel<float><<<gu, EWARPS * 32, 0, stream>>>((const float*)h, h_stride, (const float*)up, top_idx, in_w,
                                                                   (float*)act, d, ff, top);
         moe_down_kernel<float><<<gd, EWARPS * 32, 0, stream>>>((const float*)act, (const float*)down, top_idx, out_w, shared,
-                                                              nullptr, y, d, ff, top);
+                                                              nullptr, y, d, ff, top, shared_splits, shared_stride);
     } else {
         moe_up_plain_kernel<bf16><<<gu, EWARPS * 32, 0, stream>>>((const bf16*)h, h_stride, (const bf16*)up, top_idx, in_w,
                                                                  (bf16*)act, d, ff, top);
         moe_down_kernel<bf16><<<gd, EWARPS * 32, 0, stream>>>((const bf16*)act, (const bf16*)down, top_idx, out_w, shared,
-                                                             nullptr, y, d, ff, top);
+                                                             nullptr, y, d, ff, top, shared_splits, shared_stride);
     }
     return infero_check_launch("moe_experts_plain_streamed");
 }

@@ -496,21 +496,34 @@ def gated_group_norm(y: torch.Tensor, gate: Optional[torch.Tensor], weight: torc
 
 
 # ---- experts chosen by scores, ungated experts (csrc/moe.cu, csrc/moe_grouped.cu) -----------------------------------
-def moe_select_scored(logits: torch.Tensor, E: int, top: int, renorm: bool = False):
-    """From float32 logits [T, >= E]: scores sigmoid(logit); the ``top`` largest (lowest index wins a tie);
-    (top_idx int32 [T, top], top_w float32 [T, top]) with top_w the chosen scores, over their sum where ``renorm``."""
+def moe_select_scored(logits, E: int, top: int, renorm: bool = False):
+    """From float32 logits [T, >= E] (a tensor, or ``Partials``: split-K sums that are added up here): scores
+    sigmoid(logit); the ``top`` largest (lowest index wins a tie); (top_idx int32 [T, top], top_w float32 [T, top]) with
+    top_w the chosen scores, over their sum where ``renorm``."""
+    from . import Partials
+    splits, split_stride = 1, 0
+    if isinstance(logits, Partials):
+        assert logits.bias is None
+        splits, split_stride, logits = logits.splits, logits.split_stride, logits.data[0]
     T = logits.shape[0]
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= E
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    _check(lib().infero_moe_select_scored(_ptr(logits), c_int(logits.stride(0)), _ptr(idx), _ptr(w), c_int(T), c_int(E),
-                                          c_int(top), c_int(1 if renorm else 0), _stream()))
+    _check(lib().infero_moe_select_scored(_ptr(logits), c_int(logits.stride(0)), c_int(splits), c_longlong(split_stride),
+                                          _ptr(idx), _ptr(w), c_int(T), c_int(E), c_int(top), c_int(1 if renorm else 0),
+                                          _stream()))
     return idx, w
 
 
 def moe_plain_streamed(h, up, down, top_idx, top_w, weight_input: bool, shared, y) -> None:
     """y[t] = sum_c expert_c(w_c h[t]) (``weight_input``) or sum_c w_c expert_c(h[t]), expert = down(relu(up x)^2),
-    (+ shared[t]); every (token, choice) streams its expert's rows.  up [E, ff, d], down [E, d, ff]."""
+    (+ shared[t]); every (token, choice) streams its expert's rows.  up [E, ff, d], down [E, d, ff].  ``shared``:
+    float32 [T, d], or ``Partials`` of that shape (split-K sums, added up where they are used), or None."""
+    from . import Partials
+    sh_splits, sh_stride = 1, 0
+    if isinstance(shared, Partials):
+        assert shared.bias is None and tuple(shared.shape) == tuple(h.shape)
+        sh_splits, sh_stride, shared = shared.splits, shared.split_stride, shared.data[0]
     T, d = h.shape
     E, ff, _ = up.shape
     top = top_idx.shape[1]
@@ -520,7 +533,8 @@ def moe_plain_streamed(h, up, down, top_idx, top_w, weight_input: bool, shared, 
     _check(lib().infero_moe_experts_plain_streamed(_ptr(h), c_int(h.stride(0)), _ptr(up), _ptr(down), c_int(_dt(h)),
                                                    _ptr(_i32(top_idx, "top_idx")), _ptr(_f32(top_w, "top_w")),
                                                    c_int(1 if weight_input else 0), _ptr(_f32(shared, "shared")),
-                                                   _ptr(scratch), _ptr(y), c_int(T), c_int(d), c_int(ff), c_int(top), _stream()))
+                                                   c_int(sh_splits), c_longlong(sh_stride), _ptr(scratch), _ptr(y), c_int(T),
+                                                   c_int(d), c_int(ff), c_int(top), _stream()))
 
 
 def moe_plain_tc(h, up, down, top_idx, top_w, weight_input: bool, shared, y) -> None:

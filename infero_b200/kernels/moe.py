@@ -45,14 +45,22 @@ def plain_experts(h, up, down, top_idx, top_w, weight_input: bool, shared, y) ->
     weight multiplies the expert's input (``weight_input``), else sum_c w_c expert_c(h[t]); ``shared`` float32 [T, d]
     or None is added.  More pairs than experts on the bf16 path: grouped tcgen05 products; else every pair streams its
     expert."""
+    from . import Partials
     T, d = h.shape
     E, ff, _ = up.shape
     top = top_idx.shape[1]
     if (h.dtype == torch.bfloat16 and T >= GROUPED_FROM and T * top > E and d % 8 == 0 and ff % 8 == 0
             and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0 and up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0):
+        if isinstance(shared, Partials):
+            shared = shared.materialize(torch.float32)
         L.moe_plain_tc(h, up, down, top_idx, top_w, weight_input, shared, y)
         return
     step = max(1, 65535 // top)
+    if T <= step:                      # one launch: the shared expert's partial sums are added up inside it
+        L.moe_plain_streamed(h, up, down, top_idx, top_w, weight_input, shared, y)
+        return
+    if isinstance(shared, Partials):
+        shared = shared.materialize(torch.float32)
     for a in range(0, T, step):
         b = min(T, a + step)
         L.moe_plain_streamed(h[a:b], up, down, top_idx[a:b], top_w[a:b], weight_input,

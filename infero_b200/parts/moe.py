@@ -208,14 +208,14 @@ class ScoredMoe(FeedForward):
 
     def forward(self, ctx, h):
         T, d = h.shape
-        z = self.route.forward(h, out_dtype=torch.float32)
+        # few rows: the router's product and the shared expert's last product stay split-K partial sums, which the
+        # selection and the experts' last kernel add up themselves
+        z = self.route.forward(h, out_dtype=torch.float32, defer=True)
         idx, w = L.moe_select_scored(z, self.E, self.top, renorm=bool(self.spec.route_renorm))
         shared = None
         if self.shared is not None:
             shared = self.shared.forward(ctx, h)
-            if isinstance(shared, K.Partials):
-                shared = shared.materialize(torch.float32)
-            elif shared.dtype != torch.float32:
+            if not isinstance(shared, K.Partials) and shared.dtype != torch.float32:
                 shared = shared.float()
         y = torch.empty((T, d), dtype=torch.float32, device=h.device)
         from ..kernels import moe as M
